@@ -1,0 +1,281 @@
+/*
+ * kanso_cuda.h — C ABI of the B200 (sm_100a) `cuda` backend for kanso-infer's
+ * quantized-weight matmul and int8 paged decode attention.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and
+ * returns an int32 status (0 = OK). Nothing here falls back to the CPU: an
+ * unsupported shape is an error, a missing GPU is an error.
+ *
+ * Citations are file:line inside the kanso-infer source tree and name the
+ * reference interface each entry point replaces.
+ *
+ * Threading: a context is single-caller (the reference drives its engine from
+ * exactly one thread, src/server/engine_loop.rs:1-7). Calls are asynchronous on
+ * the context's stream; kanso_cuda_sync() waits for them.
+ */
+#ifndef KANSO_CUDA_H
+#define KANSO_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: the reference's EngineError variants (src/error.rs:3-11) ---- */
+#define KANSO_OK 0
+#define KANSO_ERR_CONFIG 1      /* EngineError::Config  — startup misconfiguration      */
+#define KANSO_ERR_SHAPE 2       /* EngineError::Model   — shape / bounds problems        */
+#define KANSO_ERR_UNSUPPORTED 3 /* new EngineError::Cuda — geometry the kernels lack     */
+#define KANSO_ERR_DEVICE 4      /* new EngineError::Cuda — CUDA runtime / NCCL failure    */
+#define KANSO_ERR_TIMEOUT 5     /* new EngineError::Cuda — a bounded device wait ran out  */
+
+/* ---- block formats (values are the GGML type ids of the GGUF file format) ---- */
+#define KANSO_DTYPE_Q8_0 8  /* 34 B: f16 d, 32 x int8       (src/quant/q8_0.rs:1-9 with d as f16) */
+#define KANSO_DTYPE_Q4_K 12 /* 144 B: f16 d, f16 dmin, 12 B scales, 128 B nibbles (src/quant/q4_k.rs:1-12) */
+
+#define KANSO_QK8_0 32
+#define KANSO_Q8_0_BYTES 34
+#define KANSO_QK_K 256
+#define KANSO_Q4_K_BYTES 144
+
+/* ---- activation handling of the matmul ---- */
+#define KANSO_ACT_F32 0 /* f32 activations, as scalar_dot_q8_0 / scalar_dot_q4_k (q8_0.rs:51-57, q4_k.rs:58-66) */
+#define KANSO_ACT_Q8 1  /* activations quantized per 32 by quantize_row_q8_0, int32 block sums as scalar_dot_q8_0_q8_0 (q8_0.rs:43-66) */
+
+/* ---- KV pool element type: the reference's KvCacheType flag (src/kv_cache/kind.rs:31-73) ---- */
+#define KANSO_KV_F32 0
+#define KANSO_KV_INT8 1
+#define KANSO_KV_FP8 2 /* parsed, refused with KANSO_ERR_UNSUPPORTED */
+
+typedef struct kanso_cuda_ctx kanso_cuda_ctx;
+typedef struct kanso_cuda_weight kanso_cuda_weight;
+typedef struct kanso_cuda_kv kanso_cuda_kv;
+typedef struct kanso_cuda_model kanso_cuda_model;
+
+/* Same field order and types as the reference's #[repr(C)] PagedAttentionParams
+ * (src/metal/paged_attention.rs:12-22). */
+typedef struct kanso_paged_attention_params {
+  uint32_t num_seqs;
+  uint32_t num_heads;
+  uint32_t num_kv_heads;
+  uint32_t head_dim;
+  uint32_t block_size;
+  uint32_t max_num_blocks_per_seq;
+  float scale;
+} kanso_paged_attention_params;
+
+/* The fields of the reference's ModelConfig that the decode step reads
+ * (src/config.rs:8-40; preset src/config.rs:71-90). rope_theta is a parameter
+ * because the GGUF loader overrides the preset (src/weights.rs:397-399). */
+typedef struct kanso_model_config {
+  uint32_t hidden_size;
+  uint32_t num_attention_heads;
+  uint32_t num_key_value_heads;
+  uint32_t num_hidden_layers;
+  uint32_t intermediate_size;
+  uint32_t vocab_size;
+  uint32_t block_size;
+  uint32_t max_seq_len;
+  float rms_norm_eps;
+  float rope_theta;
+} kanso_model_config;
+
+/* Names of the per-layer tensors (src/weights.rs:429-447) for kanso_cuda_model_set_weight. */
+#define KANSO_W_ATTN_Q 0
+#define KANSO_W_ATTN_K 1
+#define KANSO_W_ATTN_V 2
+#define KANSO_W_ATTN_OUTPUT 3
+#define KANSO_W_FFN_GATE 4
+#define KANSO_W_FFN_UP 5
+#define KANSO_W_FFN_DOWN 6
+#define KANSO_W_TOKEN_EMBD 7 /* layer argument ignored; also the tied lm_head (src/weights.rs:418-422) */
+#define KANSO_W_OUTPUT 8     /* layer argument ignored; optional untied lm_head */
+#define KANSO_NORM_ATTN 0
+#define KANSO_NORM_FFN 1
+#define KANSO_NORM_FINAL 2 /* layer argument ignored */
+
+/* ------------------------------------------------------------------------- */
+/* Context. Replaces the per-backend seam state the reference keeps in
+ * MetalContext (src/metal/context.rs:6-16): device, stream, scratch, counters. */
+
+/* `stream` is a cudaStream_t the caller owns (work is enqueued there), or NULL
+ * for a stream the context creates. Fails with KANSO_ERR_DEVICE when the device
+ * is absent or is not compute capability 10.x. */
+int32_t kanso_cuda_ctx_create(int32_t device, void* stream, kanso_cuda_ctx** out);
+int32_t kanso_cuda_ctx_destroy(kanso_cuda_ctx* ctx);
+int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx);
+/* Message of the last failing call on this context (or on no context when ctx
+ * is NULL: creation failures). Never NULL. */
+const char* kanso_cuda_last_error(const kanso_cuda_ctx* ctx);
+/* Kernels launched by this context since creation (the reference counts seam
+ * calls the same way, src/model.rs:246-301). */
+uint64_t kanso_cuda_launch_count(const kanso_cuda_ctx* ctx);
+/* Number of streaming multiprocessors of the context's device. */
+int32_t kanso_cuda_sm_count(const kanso_cuda_ctx* ctx);
+
+/* ------------------------------------------------------------------------- */
+/* Block kernels: src/quant. All pointers are device pointers, 16-byte aligned. */
+
+/* scalar_gemv_q8_0(weights, x, out, rows, cols) — src/quant/q8_0.rs:69-93.
+ * w: rows * cols/32 GGUF Q8_0 blocks, row-major. x f32[cols], y f32[rows].
+ * cols % 32 != 0 -> KANSO_ERR_SHAPE. */
+int32_t kanso_cuda_gemv_q8_0(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                             int64_t rows, int64_t cols);
+/* scalar_gemv_q4_k(weights, x, out, rows, cols) — src/quant/q4_k.rs:69-93.
+ * cols % 256 != 0 -> KANSO_ERR_SHAPE. */
+int32_t kanso_cuda_gemv_q4_k(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                             int64_t rows, int64_t cols);
+
+/* LinearWeight::forward, y[M,N] = x[M,K] @ W[N,K]^T — src/weights.rs:43-45,
+ * callers src/model.rs:390-397. x f32[M,K] row-major, y f32[M,N] row-major.
+ * act_mode is KANSO_ACT_F32 or KANSO_ACT_Q8 (Q4_K accepts KANSO_ACT_F32 only). */
+int32_t kanso_cuda_gemm_q8_0(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                             int64_t M, int64_t N, int64_t K, int32_t act_mode);
+int32_t kanso_cuda_gemm_q4_k(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                             int64_t M, int64_t N, int64_t K, int32_t act_mode);
+
+/* quantize_row_q8_0(xs, blocks) — src/quant/q8_0.rs:13-32,43-48. The reference's
+ * in-memory block keeps an f32 d, so the result is two planes:
+ * d_out f32[cols/32], qs_out int8[cols]. */
+int32_t kanso_cuda_quantize_row_q8_0(kanso_cuda_ctx* ctx, const float* x, float* d_out,
+                                     int8_t* qs_out, int64_t cols);
+
+/* BlockQ8_0::dequantize over nblocks GGUF blocks — src/quant/q8_0.rs:35-39. out f32[32*nblocks]. */
+int32_t kanso_cuda_dequantize_q8_0(kanso_cuda_ctx* ctx, const void* w, float* out, int64_t nblocks);
+/* BlockQ4_K::dequantize over nblocks GGUF super-blocks — src/quant/q4_k.rs:30-55. out f32[256*nblocks]. */
+int32_t kanso_cuda_dequantize_q4_k(kanso_cuda_ctx* ctx, const void* w, float* out, int64_t nblocks);
+/* get_scale_min_k4 for all 8 sub-blocks of nblocks super-blocks — src/quant/q4_k.rs:16-26.
+ * out u8[nblocks*16]: 8 scales then 8 mins per super-block. */
+int32_t kanso_cuda_unpack_scales_q4_k(kanso_cuda_ctx* ctx, const void* w, uint8_t* out,
+                                      int64_t nblocks);
+/* The int32 inner sums of scalar_dot_q8_0_q8_0 — src/quant/q8_0.rs:60-66 — for every
+ * (row, block) against activations quantized by quantize_row_q8_0.
+ * x_qs int8[cols]; isums int32[rows * cols/32]. */
+int32_t kanso_cuda_block_isums_q8_0(kanso_cuda_ctx* ctx, const void* w, const int8_t* x_qs,
+                                    int32_t* isums, int64_t rows, int64_t cols);
+
+/* ------------------------------------------------------------------------- */
+/* Weights resident on the device: LinearWeight::to_device rebuilding the block
+ * storage from raw bytes — src/weights.rs:140-158. */
+
+/* host_bytes: rows * cols/blk blocks in GGUF layout (host memory). */
+int32_t kanso_cuda_weight_upload(kanso_cuda_ctx* ctx, const void* host_bytes, size_t nbytes,
+                                 int32_t dtype, int64_t rows, int64_t cols,
+                                 kanso_cuda_weight** out);
+int32_t kanso_cuda_weight_free(kanso_cuda_weight* w);
+/* Device address of the blocks (for the pointer-level entry points above). */
+const void* kanso_cuda_weight_ptr(const kanso_cuda_weight* w);
+/* Model::linear(w, x) with host activations — src/model.rs:390-397: copies
+ * x_host f32[M,K] to the device, runs the matmul, copies y f32[M,N] back and
+ * synchronises. This is the call whose timing is the end-to-end figure. */
+int32_t kanso_cuda_linear_host(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
+                               const float* x_host, float* y_host, int64_t M, int32_t act_mode);
+/* Same with device activations, asynchronous. */
+int32_t kanso_cuda_linear(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const float* x,
+                          float* y, int64_t M, int32_t act_mode);
+/* LinearWeight::embed — src/weights.rs:50-57: dequantise the selected rows.
+ * ids u32[T] (device), out f32[T, cols] (device). An id >= rows -> KANSO_ERR_SHAPE
+ * is reported by the device status word at the next kanso_cuda_sync. */
+int32_t kanso_cuda_embed(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const uint32_t* ids,
+                         float* out, int64_t T);
+
+/* ------------------------------------------------------------------------- */
+/* KV pool: KvStorageKind with the KvCacheType flag — src/kv_cache/kind.rs:176-494,
+ * int8 pool src/kv_cache/quantized_storage.rs. */
+
+/* QuantizedKvStorage::new — quantized_storage.rs:56-105. New blocks hold quants 0
+ * and scales 1.0 (quantized_storage.rs:24-33). kv_type KANSO_KV_FP8 -> UNSUPPORTED. */
+int32_t kanso_cuda_kv_create(kanso_cuda_ctx* ctx, uint32_t num_layers, uint32_t num_blocks,
+                             uint32_t block_size, uint32_t num_kv_heads, uint32_t head_dim,
+                             int32_t kv_type, kanso_cuda_kv** out);
+int32_t kanso_cuda_kv_destroy(kanso_cuda_kv* kv);
+/* KvStorageKind::write_kv_slots — kind.rs:348; per token quantize_head_slice +
+ * write_quantized_kv_token — quantized_storage.rs:143-204,452-469.
+ * slots u32[T] (slot = block*block_size + offset, kind.rs:111), k,v f32[T,kvh,hd], all device.
+ * host_slots (optional, may be NULL) lets the call bounds-check on the host like
+ * KvSlotPlan::new (kind.rs:123-147); device-side the check sets the status word. */
+int32_t kanso_cuda_kv_write_slots(kanso_cuda_ctx* ctx, kanso_cuda_kv* kv, uint32_t layer,
+                                  const uint32_t* slots, const float* k, const float* v,
+                                  int64_t T, const uint32_t* host_slots);
+/* QuantizedKvStorage::reset_block — quantized_storage.rs:134-140: all layers. */
+int32_t kanso_cuda_kv_reset_block(kanso_cuda_ctx* ctx, kanso_cuda_kv* kv, uint32_t block);
+/* read_quantized_kv_token — quantized_storage.rs:219-270. Copies one token's
+ * stored form to host: k_q,v_q int8[kvh*hd] (may be NULL), k_scale,v_scale f32[kvh]
+ * (may be NULL), k_deq,v_deq f32[kvh*hd] = (f32)q*scale (may be NULL). Synchronous. */
+int32_t kanso_cuda_kv_read_token(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                                 uint32_t block, uint32_t offset, int8_t* k_q, int8_t* v_q,
+                                 float* k_scale, float* v_scale, float* k_deq, float* v_deq);
+/* QuantizedKvStorage::memory_bytes_per_token — quantized_storage.rs:414-419. */
+uint64_t kanso_cuda_kv_bytes_per_token(const kanso_cuda_kv* kv);
+
+/* Decode attention over the pool through the block table: the call the reference
+ * makes as metal_paged_attention / encode_paged_attention_v2
+ * (src/model.rs:874-914, src/metal/paged_attention.rs:193-203), with the math of
+ * cpu_paged_attention (paged_attention.rs:84-178) over the dequantised int8 pool
+ * (quantized_storage.rs:284-383). q f32[num_seqs, num_heads, head_dim],
+ * block_tables u32[num_seqs*max_blocks], context_lens u32[num_seqs],
+ * out f32[num_seqs, num_heads*head_dim]; all device. host_context_lens (optional)
+ * enables the reference's host checks: ctx 0 and ctx > capacity are rejected
+ * (paged_attention.rs:343-355). */
+int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                                   const float* q, const uint32_t* block_tables,
+                                   const uint32_t* context_lens, float* out,
+                                   const kanso_paged_attention_params* params,
+                                   const uint32_t* host_context_lens);
+/* validate_paged_attention_params — src/metal/paged_attention.rs:39-81 (no device work). */
+int32_t kanso_cuda_validate_paged_attention_params(const kanso_paged_attention_params* params,
+                                                   char* msg, size_t msg_len);
+
+/* ------------------------------------------------------------------------- */
+/* Glue ops of the decode step (src/model.rs:653-737,367-382; CPU statements in
+ * src/metal/ops.rs:10-77). Device pointers, asynchronous. */
+int32_t kanso_cuda_rmsnorm(kanso_cuda_ctx* ctx, const float* x, const float* weight, float* out,
+                           int64_t rows, int64_t hidden, float eps);
+/* Rotate-half RoPE in place on x f32[T, heads, head_dim] with positions u32[T]. */
+int32_t kanso_cuda_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, int64_t T,
+                        int64_t heads, int64_t head_dim, float theta);
+int32_t kanso_cuda_silu_mul(kanso_cuda_ctx* ctx, const float* gate, const float* up, float* out,
+                            int64_t n);
+int32_t kanso_cuda_residual_add(kanso_cuda_ctx* ctx, float* hidden, const float* proj, int64_t n);
+
+/* ------------------------------------------------------------------------- */
+/* Whole decode step: Model::forward_decode_step / forward_batch on a pure-decode
+ * batch — src/model.rs:1101-1231,1360-1369,1418-1740. */
+int32_t kanso_cuda_model_create(kanso_cuda_ctx* ctx, const kanso_model_config* cfg,
+                                kanso_cuda_model** out);
+int32_t kanso_cuda_model_destroy(kanso_cuda_model* m);
+/* Projection weights: GGUF blocks in host memory (copied to the device). */
+int32_t kanso_cuda_model_set_weight(kanso_cuda_model* m, uint32_t layer, int32_t which,
+                                    const void* host_bytes, size_t nbytes, int32_t dtype,
+                                    int64_t rows, int64_t cols);
+/* Norm weights: f32[hidden] in host memory. */
+int32_t kanso_cuda_model_set_norm(kanso_cuda_model* m, uint32_t layer, int32_t which,
+                                  const float* host_weight, int64_t n);
+/* One decode token per sequence. tokens, positions u32[B]; slots u32[B];
+ * block_tables u32[B*max_blocks] padded as PaddedDecodeTables (src/model.rs:64-116);
+ * context_lens u32[B] (= position + 1); all HOST arrays. logits_out f32[B, vocab] HOST.
+ * Synchronous: copies the step's inputs in, runs, copies the logits back. */
+int32_t kanso_cuda_decode_step(kanso_cuda_ctx* ctx, kanso_cuda_model* m, kanso_cuda_kv* kv,
+                               const uint32_t* tokens, const uint32_t* positions,
+                               const uint32_t* slots, const uint32_t* block_tables,
+                               const uint32_t* context_lens, uint32_t B, uint32_t max_blocks,
+                               int32_t act_mode, float* logits_out);
+/* Same step, logits left on the device (f32[B,vocab]), asynchronous; inputs are device arrays.
+ * max_ctx bounds the context lengths (sizes the split of the attention work). */
+int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, kanso_cuda_kv* kv,
+                                      const uint32_t* tokens, const uint32_t* positions,
+                                      const uint32_t* slots, const uint32_t* block_tables,
+                                      const uint32_t* context_lens, uint32_t B,
+                                      uint32_t max_blocks, uint32_t max_ctx, int32_t act_mode,
+                                      float* logits_dev);
+/* sampler::greedy_token — src/sampler.rs:7-17 (first maximum wins). logits f32[B,vocab]
+ * device, out u32[B] device. */
+int32_t kanso_cuda_greedy_token(kanso_cuda_ctx* ctx, const float* logits, uint32_t* out,
+                                int64_t B, int64_t vocab);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KANSO_CUDA_H */

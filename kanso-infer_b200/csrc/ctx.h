@@ -1,0 +1,56 @@
+// Internal definition of the context and of the handles behind the C ABI.
+#pragma once
+#include <cstdarg>
+#include <cstdio>
+#include <vector>
+
+#include "common.cuh"
+
+struct kanso_cuda_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 0;
+  int smem_optin = 0;      // max dynamic shared memory per block (opt-in), bytes
+  int* dev_status = nullptr;  // one int on the device, OR of kanso::DevStatus
+  uint64_t launches = 0;
+  std::string last_error;
+  // Scratch owned by the context (split-KV partials, staged activations). Grows on demand.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // Pinned host staging + device staging for the host-buffer entry points.
+  void* pinned = nullptr;
+  size_t pinned_bytes = 0;
+  void* stage_dev = nullptr;
+  size_t stage_dev_bytes = 0;
+};
+
+struct kanso_cuda_weight {
+  kanso_cuda_ctx* ctx = nullptr;
+  void* dev = nullptr;
+  size_t nbytes = 0;
+  int32_t dtype = 0;
+  int64_t rows = 0, cols = 0;
+};
+
+namespace kanso {
+
+int32_t fail(kanso_cuda_ctx* ctx, int32_t code, const char* fmt, ...);
+// Turns a CUDA runtime error into KANSO_ERR_DEVICE with its message.
+int32_t cuda_fail(kanso_cuda_ctx* ctx, cudaError_t e, const char* what);
+// Makes sure ctx->scratch holds at least `bytes`; nullptr + error on failure.
+void* ctx_scratch(kanso_cuda_ctx* ctx, size_t bytes);
+int32_t ctx_pinned(kanso_cuda_ctx* ctx, size_t bytes);
+int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes);
+// Checks the launch, counts it.
+int32_t after_launch(kanso_cuda_ctx* ctx, const char* what);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define KANSO_CUDA_TRY(ctx, expr, what)                          \
+  do {                                                           \
+    cudaError_t _e = (expr);                                     \
+    if (_e != cudaSuccess) return kanso::cuda_fail(ctx, _e, what); \
+  } while (0)
+
+}  // namespace kanso

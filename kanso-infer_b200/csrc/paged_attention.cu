@@ -1,0 +1,393 @@
+// Decode attention over the int8 KV pool, read through the block table.
+//
+// Math: cpu_paged_attention (src/metal/paged_attention.rs:84-178) on rows
+// dequantised as (f32)q * scale (src/kv_cache/quantized_storage.rs:284-383).
+// Nothing is materialised: no dequantised history, no score matrix.
+//
+// Stage 1, one CTA per (context partition, kv head, sequence): all query heads
+// of the GQA group are served together so each K/V byte is read once.
+//   * QK: one thread per token. The query rows are split into two int8 planes
+//     (q ~= d*(hi + lo/254)), so the dot with the int8 K row is dp4a on the
+//     packed bytes; the token's f32 K scale, the query scale and the softmax
+//     scale multiply the int32 sum once.
+//   * online softmax inside the partition (max, exp, sum) in shared memory.
+//   * PV: threads tile (dim word, token slice); V bytes are widened with one
+//     byte-permute each and accumulated in f32 with weight p * v_scale.
+//   Emits the unnormalised accumulator and (max, sum) per partition.
+// Stage 2 merges the partitions: out = sum acc_p e^{m_p-M} / sum l_p e^{m_p-M}.
+#include "glue.cuh"
+#include "kv_pool.h"
+
+namespace kanso {
+
+constexpr int PA_THREADS = 128;
+constexpr int PA_MAX_GROUP = 8;      // MAX_KV_GROUP_SIZE, src/metal/paged_attention.rs:10
+constexpr int PA_MAX_HEAD_DIM = 256; // MAX_HEAD_DIM, src/metal/paged_attention.rs:8
+
+struct PaArgs {
+  KvGeom g;
+  uint32_t layer;
+  const float* q;
+  const uint32_t* tables;
+  const uint32_t* lens;
+  float* out;
+  float* part_acc;  // [seq][head][part][hd]
+  float* part_ml;   // [seq][head][part][2]
+  uint32_t num_heads, max_blocks, part_tokens, num_parts;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
+  // biased_word = bytes ^ 0x80 (value + 128). Put byte k into the low mantissa bits of 2^23.
+  uint32_t bits = __byte_perm(biased_word, 0x4B000000u, 0x7540 | k);
+  return __uint_as_float(bits) - 8388736.0f;  // 2^23 + 128
+}
+
+template <int G>
+__global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const uint32_t hd = a.g.head_dim, bs = a.g.block_size;
+  const uint32_t part = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const uint32_t ctx = a.lens[seq];
+  const uint32_t t0 = part * a.part_tokens;
+  if (t0 >= ctx) return;
+  const uint32_t n = min(a.part_tokens, ctx - t0);
+  const int tid = threadIdx.x;
+
+  // shared: q planes, q scales, block ids, probabilities, reduction scratch
+  int8_t* qhi = reinterpret_cast<int8_t*>(smem);            // [G][hd]
+  int8_t* qlo = qhi + G * hd;                                // [G][hd]
+  float* qd = reinterpret_cast<float*>(qlo + G * hd);        // [G] (d/254)
+  uint32_t* blk = reinterpret_cast<uint32_t*>(qd + PA_MAX_GROUP);  // [part_tokens/bs + 1]
+  const uint32_t nblk_part = ((a.part_tokens + bs - 1) / bs + 4) & ~3u;
+  float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
+  float* red = prob + ((G * a.part_tokens + 3) & ~3u);       // PV scratch, 16-byte aligned
+  __shared__ float s_red[32];
+
+  // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int gq = warp; gq < G; gq += PA_THREADS / 32) {
+      const float* qrow = a.q + ((size_t)seq * a.num_heads + (size_t)kvh * G + gq) * hd;
+      float amax = 0.f;
+      for (uint32_t d = lane; d < hd; d += 32) amax = fmaxf(amax, fabsf(qrow[d]));
+#pragma unroll
+      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      float d_ = amax / 127.0f;
+      float id = d_ != 0.f ? 1.0f / d_ : 0.f;
+      for (uint32_t d = lane; d < hd; d += 32) {
+        float x = qrow[d];
+        float h = fminf(fmaxf(rintf(x * id), -127.f), 127.f);
+        float l = fminf(fmaxf(rintf(fmaf(-d_, h, x) * (254.0f * id)), -127.f), 127.f);
+        qhi[gq * hd + d] = (int8_t)h;
+        qlo[gq * hd + d] = (int8_t)l;
+      }
+      if (lane == 0) qd[gq] = d_ * (1.0f / 254.0f);
+    }
+    // physical blocks of this partition (bounds-checked once)
+    const uint32_t first_blk = t0 / bs;
+    const uint32_t last_blk = (t0 + n - 1) / bs;
+    for (uint32_t b = first_blk + tid; b <= last_blk; b += PA_THREADS) {
+      uint32_t phys = a.tables[(size_t)seq * a.max_blocks + b];
+      if (phys >= a.g.num_blocks) {
+        atomicOr(a.status, DEV_BAD_INDEX);
+        phys = 0;
+      }
+      blk[b - first_blk] = phys;
+    }
+  }
+  __syncthreads();
+  const uint32_t first_blk = t0 / bs;
+
+  // --- QK: one thread per token
+  float lmax[G];
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) lmax[gq] = -INFINITY;
+  for (uint32_t i = tid; i < n; i += PA_THREADS) {
+    const uint32_t t = t0 + i;
+    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
+    const uint32_t off = t % bs;
+    const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
+    const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
+    int ih[G], il[G];
+#pragma unroll
+    for (int gq = 0; gq < G; ++gq) ih[gq] = il[gq] = 0;
+    for (uint32_t c = 0; c < hd / 16; ++c) {
+      const uint4 kw = __ldg(krow + c);
+#pragma unroll
+      for (int gq = 0; gq < G; ++gq) {
+        const uint4 h4 = *reinterpret_cast<const uint4*>(qhi + gq * hd + 16 * c);
+        const uint4 l4 = *reinterpret_cast<const uint4*>(qlo + gq * hd + 16 * c);
+        ih[gq] = dp4a_ss((int)kw.x, (int)h4.x, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.y, (int)h4.y, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.z, (int)h4.z, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.w, (int)h4.w, ih[gq]);
+        il[gq] = dp4a_ss((int)kw.x, (int)l4.x, il[gq]);
+        il[gq] = dp4a_ss((int)kw.y, (int)l4.y, il[gq]);
+        il[gq] = dp4a_ss((int)kw.z, (int)l4.z, il[gq]);
+        il[gq] = dp4a_ss((int)kw.w, (int)l4.w, il[gq]);
+      }
+    }
+#pragma unroll
+    for (int gq = 0; gq < G; ++gq) {
+      float sc = (float)(ih[gq] * 254 + il[gq]) * (qd[gq] * ksc) * a.scale;
+      prob[gq * a.part_tokens + i] = sc;
+      lmax[gq] = fmaxf(lmax[gq], sc);
+    }
+  }
+  // --- softmax inside the partition
+  float pmax[G], psum[G];
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) pmax[gq] = block_max(lmax[gq], s_red);
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) psum[gq] = 0.f;
+  for (uint32_t i = tid; i < n; i += PA_THREADS) {
+    const uint32_t t = t0 + i;
+    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
+    const float vsc = reinterpret_cast<const float*>(rec + a.g.vs_off())[t % bs];
+#pragma unroll
+    for (int gq = 0; gq < G; ++gq) {
+      float e = expf(prob[gq * a.part_tokens + i] - pmax[gq]);
+      psum[gq] += e;
+      prob[gq * a.part_tokens + i] = e * vsc;  // weight applied to the raw int8 V row
+    }
+  }
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) psum[gq] = block_sum(psum[gq], s_red);
+  __syncthreads();
+
+  // --- PV: thread = (dim word c, token slice)
+  const uint32_t words = hd / 4;              // 4 dims per 32-bit word
+  const uint32_t nslice = PA_THREADS / words; // hd in {16..256} -> words in {4..64}
+  const uint32_t c = tid % words, slice = tid / words;
+  float acc[G][4];
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) acc[gq][0] = acc[gq][1] = acc[gq][2] = acc[gq][3] = 0.f;
+  for (uint32_t i = slice; i < n; i += nslice) {
+    const uint32_t t = t0 + i;
+    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
+    const uint32_t vw = __ldg(reinterpret_cast<const uint32_t*>(rec + a.g.v_off() +
+                                                               (size_t)(t % bs) * hd) + c) ^
+                        0x80808080u;
+    const float f0 = s8_to_f32(vw, 0), f1 = s8_to_f32(vw, 1), f2 = s8_to_f32(vw, 2),
+                f3 = s8_to_f32(vw, 3);
+#pragma unroll
+    for (int gq = 0; gq < G; ++gq) {
+      const float p = prob[gq * a.part_tokens + i];
+      acc[gq][0] = fmaf(p, f0, acc[gq][0]);
+      acc[gq][1] = fmaf(p, f1, acc[gq][1]);
+      acc[gq][2] = fmaf(p, f2, acc[gq][2]);
+      acc[gq][3] = fmaf(p, f3, acc[gq][3]);
+    }
+  }
+  // reduce over token slices through shared memory: red[slice][G][hd]
+  float4* red4 = reinterpret_cast<float4*>(red);
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq)
+    red4[(slice * G + gq) * words + c] =
+        make_float4(acc[gq][0], acc[gq][1], acc[gq][2], acc[gq][3]);
+  __syncthreads();
+  for (uint32_t e = tid; e < G * hd; e += PA_THREADS) {
+    float s = 0.f;
+    for (uint32_t sl = 0; sl < nslice; ++sl) s += red[sl * G * hd + e];
+    const uint32_t gq = e / hd, d = e % hd;
+    const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
+    a.part_acc[(head * a.num_parts + part) * hd + d] = s;
+  }
+  if (tid < G) {
+    const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + tid;
+    float m = 0.f, l = 0.f;
+#pragma unroll
+    for (int gq = 0; gq < G; ++gq)
+      if (gq == tid) {
+        m = pmax[gq];
+        l = psum[gq];
+      }
+    a.part_ml[(head * a.num_parts + part) * 2 + 0] = m;
+    a.part_ml[(head * a.num_parts + part) * 2 + 1] = l;
+  }
+}
+
+// Stage 2: merge the partitions of one (sequence, head)
+// (paged_attention_v2_reduce_kernel's role, src/metal/kernels/paged_attention_v2.metal:154-205).
+__global__ void paged_attn_stage2(const PaArgs a) {
+  const uint32_t head = blockIdx.x, seq = blockIdx.y, hd = a.g.head_dim;
+  const uint32_t ctx = a.lens[seq];
+  const size_t hidx = (size_t)seq * a.num_heads + head;
+  float* o = a.out + hidx * hd;
+  if (ctx == 0) {  // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
+    for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) o[d] = 0.f;
+    return;
+  }
+  const uint32_t np = (ctx + a.part_tokens - 1) / a.part_tokens;
+  const float* ml = a.part_ml + hidx * a.num_parts * 2;
+  float M = -INFINITY;
+  for (uint32_t p = 0; p < np; ++p) M = fmaxf(M, ml[2 * p]);
+  float denom = 0.f;
+  for (uint32_t p = 0; p < np; ++p) denom += ml[2 * p + 1] * expf(ml[2 * p] - M);
+  const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+  for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) {
+    float s = 0.f;
+    for (uint32_t p = 0; p < np; ++p)
+      s += a.part_acc[(hidx * a.num_parts + p) * hd + d] * expf(ml[2 * p] - M);
+    o[d] = s * inv;
+  }
+}
+
+static int32_t validate_params(const kanso_paged_attention_params* p, char* msg, size_t n) {
+  auto bad = [&](const char* fmt, unsigned a0 = 0, unsigned a1 = 0) {
+    if (msg && n) snprintf(msg, n, fmt, a0, a1);
+    return KANSO_ERR_UNSUPPORTED;
+  };
+  if (!p) return bad("paged attention: params is NULL");
+  if (p->num_seqs == 0 || p->num_heads == 0 || p->num_kv_heads == 0)
+    return bad("paged attention: empty shape");
+  if (p->num_heads % p->num_kv_heads != 0)
+    return bad("paged attention: num_heads %u not divisible by num_kv_heads %u", p->num_heads,
+               p->num_kv_heads);
+  unsigned group = p->num_heads / p->num_kv_heads;
+  if (group > PA_MAX_GROUP)
+    return bad("paged attention: GQA group size %u exceeds kernel limit %u", group, PA_MAX_GROUP);
+  if (p->head_dim == 0 || p->head_dim > PA_MAX_HEAD_DIM)
+    return bad("paged attention: head_dim %u outside kernel range 1..=%u", p->head_dim,
+               PA_MAX_HEAD_DIM);
+  if (p->block_size == 0 || p->max_num_blocks_per_seq == 0)
+    return bad("paged attention: block_size %u / max_num_blocks_per_seq %u must be non-zero",
+               p->block_size, p->max_num_blocks_per_seq);
+  uint64_t cap = (uint64_t)p->max_num_blocks_per_seq * p->block_size;
+  if (cap > 0xFFFFFFFFull) cap = 0xFFFFFFFFull;
+  uint64_t parts = (cap + 255) / 256;
+  if (parts < 1) parts = 1;
+  if ((uint64_t)p->num_seqs * p->num_heads * parts * p->head_dim > (1ull << 31))
+    return bad("paged attention: partial elements exceed 32-bit kernel indexing");
+  return KANSO_OK;
+}
+
+template <int G>
+static void launch_stage1(const PaArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  cudaFuncSetAttribute(paged_attn_stage1<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       (int)smem);
+  paged_attn_stage1<G><<<grid, PA_THREADS, smem, s>>>(a);
+}
+
+int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                               const float* q, const uint32_t* tables, const uint32_t* lens,
+                               float* out, const kanso_paged_attention_params* p,
+                               uint32_t max_ctx_hint) {
+  KvGeom g = kv_geom(kv);
+  const uint32_t G = p->num_heads / p->num_kv_heads;
+  const uint32_t hd = p->head_dim;
+  // partition size: enough CTAs to cover the SMs, but no smaller than 64 tokens
+  uint64_t cap = (uint64_t)p->max_num_blocks_per_seq * p->block_size;
+  if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
+  uint32_t pt = 512;
+  while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
+                        2ull * ctx->sm_count)
+    pt >>= 1;
+  // whole blocks per partition keep the per-partition block list simple
+  if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
+  const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
+
+  const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
+  const size_t acc_bytes = nheads_total * nparts * hd * sizeof(float);
+  const size_t ml_bytes = nheads_total * nparts * 2 * sizeof(float);
+  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, acc_bytes + ml_bytes + 256);
+  if (!scratch) return KANSO_ERR_DEVICE;
+
+  PaArgs a;
+  a.g = g;
+  a.layer = layer;
+  a.q = q;
+  a.tables = tables;
+  a.lens = lens;
+  a.out = out;
+  a.part_acc = reinterpret_cast<float*>(scratch);
+  a.part_ml = reinterpret_cast<float*>(scratch + ((acc_bytes + 255) & ~size_t(255)));
+  a.num_heads = p->num_heads;
+  a.max_blocks = p->max_num_blocks_per_seq;
+  a.part_tokens = pt;
+  a.num_parts = nparts;
+  a.scale = p->scale;
+  a.status = ctx->dev_status;
+
+  const uint32_t nblk_part = ((pt + p->block_size - 1) / p->block_size + 4) & ~3u;
+  const uint32_t words = hd / 4, nslice = PA_THREADS / words;
+  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4;
+  size_t red_bytes = (size_t)nslice * G * hd * 4;
+  if (red_bytes < 128) red_bytes = 128;
+  smem += red_bytes;
+  if (smem > (size_t)ctx->smem_optin)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: %zu bytes of shared memory needed",
+                smem);
+  dim3 grid(nparts, p->num_kv_heads, p->num_seqs);
+  switch (G) {
+    case 1: launch_stage1<1>(a, grid, smem, ctx->stream); break;
+    case 2: launch_stage1<2>(a, grid, smem, ctx->stream); break;
+    case 3: launch_stage1<3>(a, grid, smem, ctx->stream); break;
+    case 4: launch_stage1<4>(a, grid, smem, ctx->stream); break;
+    case 5: launch_stage1<5>(a, grid, smem, ctx->stream); break;
+    case 6: launch_stage1<6>(a, grid, smem, ctx->stream); break;
+    case 7: launch_stage1<7>(a, grid, smem, ctx->stream); break;
+    default: launch_stage1<8>(a, grid, smem, ctx->stream); break;
+  }
+  int32_t st = after_launch(ctx, "paged_attention stage 1");
+  if (st) return st;
+  paged_attn_stage2<<<dim3(p->num_heads, p->num_seqs), 64, 0, ctx->stream>>>(a);
+  return after_launch(ctx, "paged_attention stage 2");
+}
+
+}  // namespace kanso
+
+using namespace kanso;
+
+extern "C" {
+
+int32_t kanso_cuda_validate_paged_attention_params(const kanso_paged_attention_params* params,
+                                                   char* msg, size_t msg_len) {
+  return validate_params(params, msg, msg_len);
+}
+
+int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                                   const float* q, const uint32_t* block_tables,
+                                   const uint32_t* context_lens, float* out,
+                                   const kanso_paged_attention_params* params,
+                                   const uint32_t* host_context_lens) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "paged_attention: ctx is NULL");
+  char msg[256];
+  int32_t st = validate_params(params, msg, sizeof msg);
+  if (st) return fail(ctx, st, "%s", msg);
+  if (!kv || !q || !block_tables || !context_lens || !out)
+    return fail(ctx, KANSO_ERR_SHAPE, "paged_attention: NULL pointer");
+  if (layer >= kv->layers)
+    return fail(ctx, KANSO_ERR_SHAPE, "Layer index %u out of bounds (%u)", layer, kv->layers);
+  if (params->num_kv_heads != kv->kv_heads || params->head_dim != kv->head_dim ||
+      params->block_size != kv->block_size)
+    return fail(ctx, KANSO_ERR_SHAPE,
+                "paged attention: params (kv_heads %u, head_dim %u, block_size %u) do not match "
+                "the pool (%u, %u, %u)",
+                params->num_kv_heads, params->head_dim, params->block_size, kv->kv_heads,
+                kv->head_dim, kv->block_size);
+  const uint32_t hd = params->head_dim;
+  if (hd < 16 || (hd & (hd - 1)) != 0)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                "paged attention: head_dim %u is not one of 16, 32, 64, 128, 256", hd);
+  uint32_t max_ctx = 0;
+  if (host_context_lens) {
+    // gpu_paged_attention_v2 rejects these on the host (src/metal/paged_attention.rs:343-355)
+    uint64_t cap = (uint64_t)params->max_num_blocks_per_seq * params->block_size;
+    for (uint32_t s = 0; s < params->num_seqs; ++s) {
+      if (host_context_lens[s] == 0)
+        return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: sequence %u has context 0", s);
+      if (host_context_lens[s] > cap)
+        return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                    "paged attention: sequence %u context %u exceeds table capacity %llu", s,
+                    host_context_lens[s], (unsigned long long)cap);
+      if (host_context_lens[s] > max_ctx) max_ctx = host_context_lens[s];
+    }
+  }
+  return launch_paged_attention(ctx, kv, layer, q, block_tables, context_lens, out, params,
+                                max_ctx);
+}
+
+}  // extern "C"
