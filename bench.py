@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Headline measurement: Q4_K batch-1 decode GEMV, HBM GB/s on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): W_up[14336x4096] and W_down[4096x14336], GGUF
+Q4_K super-blocks quantised from seeded N(0, 0.02) weights, f32 activations from
+N(0, 1), y = W.x. One step = one GEMV over each matrix of a ring of distinct
+(up, down) pairs whose total size is several times the 126 MB L2, so every launch
+streams its weights from HBM. The step is captured in a CUDA graph so that the
+~5 us kernels run back to back instead of at the host's launch rate.
+
+Prints ONE JSON line (rank 0). `value` counts algorithmic bytes
+(weights once + x + y per launch) over the device time of the timed steps.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+UP = (14336, 4096)    # rows (N), cols (K)
+DOWN = (4096, 14336)
+Q4K_BYTES, QK_K = 144, 256
+SEED = 0xB2000000 + 2 * 100
+
+
+def alg_bytes(rows, cols):
+    """Weights once + x + y, the byte count the reference's own probe uses
+    (src/bench/probes.rs:84-86)."""
+    return rows * (cols // QK_K) * Q4K_BYTES + 4 * cols + 4 * rows
+
+
+def make_weights(oracle, rows, cols, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    return oracle.quantize_weights_q4_k(w)
+
+
+def ring_of_weights(base, copies, rows, cols, seed):
+    """`copies` distinct block matrices: the first is quantised from N(0, 0.02) by the oracle's
+    encoder, the others are row rotations of it (different bytes at every address, same
+    distribution), which keeps host set-up time short."""
+    blocks = base.reshape(rows, -1)
+    out = [base]
+    rng = np.random.Generator(np.random.PCG64(seed + 7))
+    for _ in range(copies - 1):
+        out.append(np.ascontiguousarray(np.roll(blocks, int(rng.integers(1, rows)), axis=0))
+                   .reshape(-1))
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc, self.lines, self.idx = None, [], gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.idx), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def cpu_gemv_time(oracle, blocks, x, rows, cols, repeats):
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        oracle.gemv_q4_k(blocks, x, rows, cols)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline_1core(oracle, up, down, xs):
+    """The reference's scalar row loop is single-threaded (src/quant/q4_k.rs:69-93): 1 core."""
+    t_once = cpu_gemv_time(oracle, up, xs[0], *UP, 1) + cpu_gemv_time(oracle, down, xs[1], *DOWN, 1)
+    passes = max(1, min(200, int(12.0 / max(t_once, 1e-3))))
+    t = cpu_gemv_time(oracle, up, xs[0], *UP, passes) + cpu_gemv_time(oracle, down, xs[1], *DOWN,
+                                                                      passes)
+    nbytes = passes * (alg_bytes(*UP) + alg_bytes(*DOWN))
+    return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"{passes} passes of the up and down GEMV ({2 * passes} calls, {t:.1f} s) "
+                      "through the scalar restatement of scalar_gemv_q4_k"}
+
+
+def threaded_cpu_step(oracle, mats, threads):
+    """One step on the host: every GEMV split by rows over `threads` threads (ctypes releases
+    the GIL). mats: list of (blocks, x, rows, cols)."""
+    def work(blocks, x, rows, cols, r0, r1):
+        bpr = cols // QK_K * Q4K_BYTES
+        oracle.gemv_q4_k(blocks[r0 * bpr:r1 * bpr], x, r1 - r0, cols)
+
+    for blocks, x, rows, cols in mats:
+        cuts = [rows * i // threads for i in range(threads + 1)]
+        ts = [threading.Thread(target=work, args=(blocks, x, rows, cols, cuts[i], cuts[i + 1]))
+              for i in range(threads)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+
+def run_reference(args):
+    """The reference's CPU path for this workload: scalar_gemv_q4_k restated in oracle/ (the
+    reference is a Rust crate and no Rust toolchain exists here, so its own binary cannot
+    run). The row loop is split over all host threads; each step is one (up, down) pair."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    cores = os.cpu_count() or 1
+    up = make_weights(O, *UP, SEED + 1)
+    down = make_weights(O, *DOWN, SEED + 2)
+    rng = np.random.Generator(np.random.PCG64(SEED + 3))
+    xs = [rng.standard_normal(UP[1]).astype(np.float32),
+          rng.standard_normal(DOWN[1]).astype(np.float32)]
+    mats = [(up, xs[0], *UP), (down, xs[1], *DOWN)]
+    for _ in range(args.warmup):
+        threaded_cpu_step(O, mats, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        threaded_cpu_step(O, mats, cores)
+    dt = time.perf_counter() - t0
+    nbytes = args.steps * (alg_bytes(*UP) + alg_bytes(*DOWN))
+    val = nbytes / dt / 1e9
+    sample = ("each step = one up GEMV + one down GEMV (1 of the ring's pairs), rows split over "
+              f"{cores} threads; the reference's own loop is single-threaded")
+    print(json.dumps({
+        "impl": "reference", "metric": "Q4_K GEMV HBM GB/s", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "cfg2 Q4_K GEMV batch 1: W_up[14336x4096] + W_down[4096x14336]",
+                   "bytes_per_step": alg_bytes(*UP) + alg_bytes(*DOWN)},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    kb = importlib.import_module("kanso-infer_b200").backend
+    from oracle import oracle as O  # CPU baseline leg + a result check only
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx = kb.Context(local, stream)
+
+    pairs = args.pairs
+    up0 = make_weights(O, *UP, SEED + 1 + 10 * rank)
+    down0 = make_weights(O, *DOWN, SEED + 2 + 10 * rank)
+    ups = ring_of_weights(up0, pairs, *UP, SEED + 11)
+    downs = ring_of_weights(down0, pairs, *DOWN, SEED + 12)
+    rng = np.random.Generator(np.random.PCG64(SEED + 3))
+    x_up = rng.standard_normal(UP[1]).astype(np.float32)
+    x_down = rng.standard_normal(DOWN[1]).astype(np.float32)
+
+    W_up = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *UP) for b in ups]
+    W_down = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *DOWN) for b in downs]
+    dx_up = torch.from_numpy(x_up).cuda()
+    dx_down = torch.from_numpy(x_down).cuda()
+    y_up = torch.empty(UP[0], dtype=torch.float32, device="cuda")
+    y_down = torch.empty(DOWN[0], dtype=torch.float32, device="cuda")
+
+    def step():
+        for wu, wd in zip(W_up, W_down):
+            wu.forward(dx_up, y_up, 1)
+            wd.forward(dx_down, y_down, 1)
+
+    # result check against the oracle on the last pair (not timed)
+    step()
+    ctx.sync()
+    ref_up = O.gemv_q4_k(ups[-1], x_up, *UP)
+    err = float(np.max(np.abs(y_up.cpu().numpy() - ref_up)) / np.max(np.abs(ref_up)))
+    if err > 1e-3:
+        raise SystemExit(f"bench: GEMV result differs from the oracle by {err:.2e} (> 1e-3)")
+
+    launches_per_step = 2 * pairs
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # keep sampling for a moment so that short timed regions still get samples
+    clocks = None
+    if rank == 0:
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            graph.replay()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+
+    step_bytes = pairs * (alg_bytes(*UP) + alg_bytes(*DOWN))
+    value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
+    us_per_launch = ms * 1e3 / (args.steps * launches_per_step)
+
+    # end to end through the host-buffer call: x from host memory, y back to host memory
+    e2e = None
+    if True:
+        yh_up = np.empty(UP[0], np.float32)
+        yh_down = np.empty(DOWN[0], np.float32)
+
+        def host_step():
+            for wu, wd in zip(W_up, W_down):
+                wu.forward_host(x_up, yh_up, 1)
+                wd.forward_host(x_down, yh_down, 1)
+
+        host_step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        n_e2e = max(1, min(args.steps, 20))
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            host_step()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e = {"value": world * step_bytes * n_e2e / dt / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": pairs * 4 * (UP[1] + DOWN[1]),
+               "d2h_bytes_per_step": pairs * 4 * (UP[0] + DOWN[0]),
+               "steps": n_e2e, "us_per_call": dt / (n_e2e * launches_per_step) * 1e6}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    per_launch_bytes = (alg_bytes(*UP) + alg_bytes(*DOWN)) / 2
+    achieved = per_launch_bytes / (us_per_launch * 1e-6) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "gemv_stream_q4_k_cfg2.traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+
+    cpu = cpu_baseline_1core(O, up0, down0, [x_up, x_down]) if world == 1 else None
+    line = {
+        "metric": "Q4_K GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": "cfg2 Q4_K GEMV batch 1: W_up[14336x4096] + W_down[4096x14336]",
+                   "ring_pairs": pairs, "bytes_per_step": step_bytes,
+                   "l2": f"inputs larger than L2: {step_bytes / 1e6:.0f} MB of distinct weights "
+                         "per step vs 126 MB L2",
+                   "launch": "CUDA graph of the step", "parallelism": f"shards{world}",
+                   "check_vs_oracle_rel_err": err},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
+                     "kernel": "gemv_stream_kernel<Q4_K>", "us_per_launch": us_per_launch,
+                     "alg_bytes_per_launch": per_launch_bytes},
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--pairs", type=int, default=8, help="distinct (up, down) pairs in the ring")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 50:
+            args.steps = 50  # bounded sample: the CPU step takes ~0.1 s
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

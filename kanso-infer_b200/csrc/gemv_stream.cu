@@ -442,9 +442,14 @@ static int32_t launch_stream(kanso_cuda_ctx* ctx, const void* w, const float* x,
   a.nstage = best_s;
   StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, M, best_w, best_s, best_sb);
   auto kern = gemv_stream_kernel<FMT, MT, PLANES>;
-  KANSO_CUDA_TRY(ctx,
-                 cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total),
-                 "gemv: shared memory opt-in");
+  static int smem_set[16] = {0};  // per device: largest opt-in already made for this kernel
+  if (L.total > smem_set[ctx->device & 15]) {
+    KANSO_CUDA_TRY(ctx,
+                   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ctx->smem_optin),
+                   "gemv: shared memory opt-in");
+    smem_set[ctx->device & 15] = ctx->smem_optin;
+  }
   kern<<<grid, best_w * 32, L.total, ctx->stream>>>(a);
   return after_launch(ctx, "gemv_stream");
 }

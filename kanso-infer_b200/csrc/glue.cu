@@ -1,5 +1,7 @@
 // Element-wise pieces of the decode step: RMSNorm, rotate-half RoPE, SiLU*up,
 // residual add, greedy argmax (src/model.rs:653-737,367-382; src/sampler.rs:7-17).
+#include <cmath>
+
 #include "ctx.h"
 #include "glue.cuh"
 
@@ -20,9 +22,14 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 
 // Rotate-half RoPE in place (src/model.rs:721-737). With a table: cos/sin rows of
 // build_rope_table (src/model.rs:698-719); without: computed on the fly.
+constexpr int ROPE_MAX_HALF = 128;  // head_dim <= 256
+struct RopeFreq {
+  float f[ROPE_MAX_HALF];
+};
 __global__ void rope_kernel(float* __restrict__ x, const uint32_t* __restrict__ positions,
-                            int heads, int head_dim, float theta, const float* __restrict__ cos_t,
-                            const float* __restrict__ sin_t, int table_len, int* status) {
+                            int heads, int head_dim, const RopeFreq freq,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            int table_len, int* status) {
   int t = blockIdx.x;
   int half = head_dim / 2;
   uint32_t pos = positions[t];
@@ -37,7 +44,7 @@ __global__ void rope_kernel(float* __restrict__ x, const uint32_t* __restrict__ 
       c = cos_t[(int64_t)pos * half + j];
       s = sin_t[(int64_t)pos * half + j];
     } else {
-      float ang = (float)pos * powf(theta, -2.0f * (float)j / (float)head_dim);
+      float ang = __fmul_rn((float)pos, freq.f[j]);
       c = cosf(ang);
       s = sinf(ang);
     }
@@ -116,7 +123,11 @@ int32_t launch_rmsnorm(kanso_cuda_ctx* ctx, const float* x, const float* w, floa
 int32_t launch_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, int64_t T,
                     int64_t heads, int64_t head_dim, float theta, const float* cos_t,
                     const float* sin_t, int table_len) {
-  rope_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(x, positions, (int)heads, (int)head_dim, theta,
+  RopeFreq freq;
+  if (!cos_t)  // theta^(-2j/head_dim) with the host's powf, as build_rope_table (src/model.rs:700-707)
+    for (int j = 0; j < head_dim / 2; ++j)
+      freq.f[j] = std::pow(theta, -2.0f * (float)j / (float)head_dim);
+  rope_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(x, positions, (int)heads, (int)head_dim, freq,
                                                     cos_t, sin_t, table_len, ctx->dev_status);
   return after_launch(ctx, "rope");
 }
@@ -149,9 +160,9 @@ int32_t kanso_cuda_rmsnorm(kanso_cuda_ctx* ctx, const float* x, const float* wei
 int32_t kanso_cuda_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, int64_t T,
                         int64_t heads, int64_t head_dim, float theta) {
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "rope: ctx is NULL");
-  if (T < 0 || heads <= 0 || head_dim <= 0 || head_dim % 2)
-    return fail(ctx, KANSO_ERR_SHAPE, "rope: head_dim %lld must be even and positive",
-                (long long)head_dim);
+  if (T < 0 || heads <= 0 || head_dim <= 0 || head_dim % 2 || head_dim > 2 * ROPE_MAX_HALF)
+    return fail(ctx, KANSO_ERR_SHAPE, "rope: head_dim %lld must be even, positive and <= %d",
+                (long long)head_dim, 2 * ROPE_MAX_HALF);
   if (T == 0) return KANSO_OK;
   return launch_rope(ctx, x, positions, T, heads, head_dim, theta, nullptr, nullptr, 0);
 }

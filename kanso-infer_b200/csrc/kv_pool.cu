@@ -121,7 +121,7 @@ int32_t kanso_cuda_kv_create(kanso_cuda_ctx* ctx, uint32_t num_layers, uint32_t 
 
 int32_t kanso_cuda_kv_destroy(kanso_cuda_kv* kv) {
   if (!kv) return KANSO_OK;
-  cudaStreamSynchronize(kv->ctx->stream);
+  cudaDeviceSynchronize();  // the context may already be destroyed
   cudaFree(kv->pool);
   delete kv;
   return KANSO_OK;

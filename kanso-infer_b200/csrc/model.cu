@@ -163,7 +163,7 @@ int32_t kanso_cuda_model_create(kanso_cuda_ctx* ctx, const kanso_model_config* c
 
 int32_t kanso_cuda_model_destroy(kanso_cuda_model* m) {
   if (!m) return KANSO_OK;
-  cudaStreamSynchronize(m->ctx->stream);
+  cudaDeviceSynchronize();  // the context may already be destroyed
   free_ws(m);
   for (auto& l : m->layers) {
     for (auto& w : l.w)

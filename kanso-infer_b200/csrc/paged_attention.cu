@@ -266,8 +266,14 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
 
 template <int G>
 static void launch_stage1(const PaArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
-  cudaFuncSetAttribute(paged_attn_stage1<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       (int)smem);
+  static size_t smem_set[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > smem_set[dev & 15]) {
+    cudaFuncSetAttribute(paged_attn_stage1<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+    smem_set[dev & 15] = smem;
+  }
   paged_attn_stage1<G><<<grid, PA_THREADS, smem, s>>>(a);
 }
 

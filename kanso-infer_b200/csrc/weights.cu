@@ -77,7 +77,7 @@ int32_t kanso_cuda_weight_upload(kanso_cuda_ctx* ctx, const void* host_bytes, si
 
 int32_t kanso_cuda_weight_free(kanso_cuda_weight* w) {
   if (!w) return KANSO_OK;
-  cudaStreamSynchronize(w->ctx->stream);
+  cudaDeviceSynchronize();  // the context may already be destroyed
   cudaFree(w->dev);
   delete w;
   return KANSO_OK;

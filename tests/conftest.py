@@ -44,8 +44,11 @@ def torch_cuda():
 
 @pytest.fixture(scope="session")
 def ctx(kb, torch_cuda):
-    """A context on torch's current stream, so torch tensors and events line up with it."""
-    c = kb.Context(0, torch_cuda.cuda.current_stream())
+    """A context on a torch stream made current for the session, so torch tensors, copies
+    and events are ordered with the library's kernels."""
+    stream = torch_cuda.cuda.Stream()
+    torch_cuda.cuda.set_stream(stream)
+    c = kb.Context(0, stream)
     yield c
     c.close()
 

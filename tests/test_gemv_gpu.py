@@ -1,0 +1,162 @@
+"""GPU: streaming GEMV / few-row GEMM against the oracle.
+
+Tolerance: max|y_gpu - y_ref| / max|y_ref| <= 1e-3, the scale-relative form of
+the reference's own comparisons (tests/test_quantized_weights.rs:375-397).
+"""
+import numpy as np
+import pytest
+
+from conftest import golden, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_gemm(ctx, kb, torch, dtype, blocks, x, M, N, K, act=0):
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    wb = dev(torch, blocks)
+    xd = dev(torch, x.astype(np.float32))
+    if dtype == kb.DTYPE_Q8_0:
+        if M == 1 and act == 0:
+            ctx.gemv_q8_0(wb, xd, y, N, K)
+        else:
+            ctx.gemm_q8_0(wb, xd, y, M, N, K, act)
+    else:
+        if M == 1:
+            ctx.gemv_q4_k(wb, xd, y, N, K)
+        else:
+            ctx.gemm_q4_k(wb, xd, y, M, N, K, act)
+    ctx.sync()
+    return y.cpu().numpy()
+
+
+def gguf_q8_from_ref(d, qs):
+    """Reference-layout blocks (f32 d) -> GGUF bytes (d rounded to f16)."""
+    n = d.size
+    out = np.zeros((n, 34), np.uint8)
+    out[:, :2] = d.astype(np.float16).reshape(-1, 1).view(np.uint8)
+    out[:, 2:] = qs.reshape(n, 32).view(np.uint8)
+    return out.reshape(-1)
+
+
+def test_golden_blocks(ctx, kb, oracle, torch_cuda):
+    g = golden("gguf_blocks.npz")
+    y8 = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, g["q8_0"], g["x"][None], 1, 12, 512)
+    assert rel_err(y8[0], g["gemv_q8_0"]) <= TOL
+    y8q = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, g["q8_0"], g["x"][None], 1, 12, 512,
+                   kb.ACT_Q8)
+    assert rel_err(y8q[0], g["gemv_q8_0_q8"]) <= 1e-5  # same int32 sums, f32 order differs
+    y4 = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q4_K, g["q4_k"], g["x"][None], 1, 12, 512)
+    assert rel_err(y4[0], g["gemv_q4_k"]) <= TOL
+
+
+def test_reference_gemv_patterns(ctx, kb, oracle, torch_cuda):
+    # tests/test_neon_simd_gemv.rs:104-143 (Q8_0 64x128) in the f16-scale layout
+    g = golden("q8_0_kat.npz")
+    blocks = gguf_q8_from_ref(g["gemv_d"].reshape(-1), g["gemv_qs"])
+    ref = oracle.gemv_q8_0(blocks, g["gemv_x"], 64, 128)
+    got = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, blocks, g["gemv_x"][None], 1, 64, 128)
+    assert rel_err(got[0], ref) <= TOL
+    # tests/test_neon_simd_gemv.rs:146-188 (Q4_K 32x256)
+    k = golden("q4_k_kat.npz")
+    blk = np.zeros((32, 144), np.uint8)
+    blk[:, 0:2] = k["gemv_d"].astype(np.float16).reshape(-1, 1).view(np.uint8)
+    blk[:, 2:4] = np.frombuffer(np.float16(k["gemv_dmin"]).tobytes(), np.uint8)
+    blk[:, 4:16] = k["gemv_scales"]
+    blk[:, 16:] = k["gemv_qs"]
+    ref = oracle.gemv_q4_k(blk.reshape(-1), k["gemv_x"], 32, 256)
+    got = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q4_K, blk.reshape(-1), k["gemv_x"][None], 1, 32,
+                   256)
+    assert rel_err(got[0], ref) <= TOL
+
+
+@pytest.mark.parametrize("rows,cols", [(2560, 960), (960, 2560), (1, 32), (3, 64), (149, 992),
+                                       (300, 4096), (17, 8192), (64, 1056)])
+def test_q8_0_gemv_shapes(ctx, kb, oracle, torch_cuda, rows, cols):
+    rng = np.random.Generator(np.random.PCG64(0xB2000100 + rows * 31 + cols))
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(cols).astype(np.float32)
+    blocks = oracle.quantize_weights_q8_0(w)
+    ref = oracle.gemv_q8_0(blocks, x, rows, cols)
+    got = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, blocks, x[None], 1, rows, cols)
+    assert rel_err(got[0], ref) <= TOL
+    refq = oracle.gemv_q8_0_q8(blocks, x, rows, cols)
+    gotq = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, blocks, x[None], 1, rows, cols, kb.ACT_Q8)
+    assert rel_err(gotq[0], refq) <= 1e-5
+
+
+@pytest.mark.parametrize("rows,cols", [(14336, 4096), (4096, 14336), (1, 256), (5, 512),
+                                       (149, 768), (33, 8192), (9, 28672), (200, 2048)])
+def test_q4_k_gemv_shapes(ctx, kb, oracle, torch_cuda, rows, cols):
+    rng = np.random.Generator(np.random.PCG64(0xB2000200 + rows * 31 + cols))
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(cols).astype(np.float32)
+    blocks = oracle.quantize_weights_q4_k(w)
+    ref = oracle.gemv_q4_k(blocks, x, rows, cols)
+    got = run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q4_K, blocks, x[None], 1, rows, cols)
+    assert rel_err(got[0], ref) <= TOL
+
+
+@pytest.mark.parametrize("M", [2, 3, 4, 7, 8, 13])
+def test_few_row_gemm(ctx, kb, oracle, torch_cuda, M):
+    rng = np.random.Generator(np.random.PCG64(0xB2000300 + M))
+    N, K = 320, 1024
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b8, b4 = oracle.quantize_weights_q8_0(w), oracle.quantize_weights_q4_k(w)
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, b8, x, M, N, K),
+                   oracle.gemm_q8_0(b8, x, M, N, K)) <= TOL
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, b8, x, M, N, K, kb.ACT_Q8),
+                   oracle.gemm_q8_0(b8, x, M, N, K, 1)) <= 1e-5
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q4_K, b4, x, M, N, K),
+                   oracle.gemm_q4_k(b4, x, M, N, K)) <= TOL
+
+
+def test_linearity_at_full_size(ctx, kb, oracle, torch_cuda):
+    """Size-independent property at the benchmark shape: W(ax + by) = a Wx + b Wy."""
+    torch = torch_cuda
+    rows, cols = 14336, 4096
+    rng = np.random.Generator(np.random.PCG64(0xB2000400))
+    raw = oracle.quantize_weights_q4_k((rng.standard_normal((rows, cols)) * 0.02)
+                                       .astype(np.float32))
+    wb = dev(torch, raw)
+    x1 = torch.randn(cols, device="cuda")
+    x2 = torch.randn(cols, device="cuda")
+    ys = []
+    for x in (x1, x2, 0.5 * x1 - 2.0 * x2):
+        y = torch.empty(rows, dtype=torch.float32, device="cuda")
+        ctx.gemv_q4_k(wb, x.contiguous(), y, rows, cols)
+        ys.append(y)
+    ctx.sync()
+    comb = 0.5 * ys[0] - 2.0 * ys[1]
+    assert float((ys[2] - comb).abs().max() / comb.abs().max()) <= 2e-4
+
+
+def test_weight_handle_and_host_linear(ctx, kb, oracle, torch_cuda):
+    rng = np.random.Generator(np.random.PCG64(0xB2000500))
+    N, K, M = 640, 960, 3
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    blocks = oracle.quantize_weights_q8_0(w)
+    W = kb.Weight(ctx, blocks, kb.DTYPE_Q8_0, N, K)
+    y = np.empty((M, N), np.float32)
+    W.forward_host(x, y, M)
+    assert rel_err(y, oracle.gemm_q8_0(blocks, x, M, N, K)) <= TOL
+    # embed: selected rows, bit-exact dequant (src/weights.rs:50-57)
+    ids = np.array([5, 0, 639, 5], np.uint32)
+    out = torch_cuda.empty((4, K), dtype=torch_cuda.float32, device="cuda")
+    W.embed(dev(torch_cuda, ids), out, 4)
+    ctx.sync()
+    ref = oracle.dequantize_q8_0(blocks).reshape(N, K)[ids.astype(np.int64)]
+    assert out.cpu().numpy().tobytes() == ref.tobytes()
+    with pytest.raises(kb.KansoError) as e:
+        kb.Weight(ctx, blocks[:-1], kb.DTYPE_Q8_0, N, K)
+    assert e.value.code == kb.ERR_SHAPE
+    with pytest.raises(kb.KansoError) as e:
+        kb.Weight(ctx, blocks, kb.DTYPE_Q4_K, N, K)  # 960 % 256 != 0: a block may not straddle a row
+    assert e.value.code == kb.ERR_SHAPE
+    W.free()
