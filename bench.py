@@ -200,6 +200,10 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     ctx = kb.Context(local, stream)
+    # the weights are uploaded once and never written again: let consecutive GEMVs overlap
+    # their weight prefetch with the drain of the kernel before them
+    if not os.environ.get("KANSO_BENCH_NO_OVERLAP"):
+        ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 1)
 
     pairs = args.pairs
     up0 = make_weights(O, *UP, SEED + 1 + 10 * rank)
@@ -317,7 +321,7 @@ def run_ours(args):
     if os.path.exists(tpath):
         traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
 
-    cpu = cpu_baseline_1core(O, up0, down0, [x_up, x_down]) if world == 1 else None
+    cpu = cpu_baseline_1core(O, up0, down0, [x_up, x_down]) if (world == 1 and not os.environ.get("KANSO_BENCH_SKIP_CPU")) else None
     line = {
         "metric": "Q4_K GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,

@@ -109,6 +109,14 @@ int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx);
 /* Message of the last failing call on this context (or on no context when ctx
  * is NULL: creation failures). Never NULL. */
 const char* kanso_cuda_last_error(const kanso_cuda_ctx* ctx);
+/* Options of a context. KANSO_OPT_OVERLAP_WEIGHT_PREFETCH (default 0): the caller promises
+ * that the weight blocks given to matmul calls are not written by work enqueued earlier on
+ * the stream (they are model parameters, uploaded and left alone, as LinearWeight storage is
+ * in the reference, src/weights.rs:22). A matmul kernel may then be launched with
+ * programmatic dependent launch and fetch its first weight tiles while the kernel before it
+ * drains; it still waits for that kernel before it reads activations or writes results. */
+#define KANSO_OPT_OVERLAP_WEIGHT_PREFETCH 1
+int32_t kanso_cuda_ctx_set_option(kanso_cuda_ctx* ctx, int32_t option, int32_t value);
 /* Kernels launched by this context since creation (the reference counts seam
  * calls the same way, src/model.rs:246-301). */
 uint64_t kanso_cuda_launch_count(const kanso_cuda_ctx* ctx);

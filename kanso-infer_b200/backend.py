@@ -16,6 +16,7 @@ OK, ERR_CONFIG, ERR_SHAPE, ERR_UNSUPPORTED, ERR_DEVICE, ERR_TIMEOUT = range(6)
 DTYPE_Q8_0, DTYPE_Q4_K = 8, 12
 ACT_F32, ACT_Q8 = 0, 1
 KV_F32, KV_INT8, KV_FP8 = 0, 1, 2
+OPT_OVERLAP_WEIGHT_PREFETCH = 1
 Q8_BYTES, Q4K_BYTES = 34, 144
 (W_ATTN_Q, W_ATTN_K, W_ATTN_V, W_ATTN_OUTPUT, W_FFN_GATE, W_FFN_UP, W_FFN_DOWN, W_TOKEN_EMBD,
  W_OUTPUT) = range(9)
@@ -58,6 +59,7 @@ PROTOTYPES = {
     "kanso_cuda_ctx_destroy": (_I32, [_P]),
     "kanso_cuda_sync": (_I32, [_P]),
     "kanso_cuda_last_error": (C.c_char_p, [_P]),
+    "kanso_cuda_ctx_set_option": (_I32, [_P, _I32, _I32]),
     "kanso_cuda_launch_count": (_U64, [_P]),
     "kanso_cuda_sm_count": (_I32, [_P]),
     "kanso_cuda_gemv_q8_0": (_I32, [_P, _P, _P, _P, _I64, _I64]),
@@ -163,6 +165,9 @@ class Context:
 
     def sync(self):
         self.check(self.lib.kanso_cuda_sync(self.h))
+
+    def set_option(self, option: int, value: int):
+        self.call("kanso_cuda_ctx_set_option", option, value)
 
     @property
     def launches(self) -> int:

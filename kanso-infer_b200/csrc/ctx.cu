@@ -157,6 +157,17 @@ const char* kanso_cuda_last_error(const kanso_cuda_ctx* ctx) {
   return ctx ? ctx->last_error.c_str() : g_no_ctx_error.c_str();
 }
 
+int32_t kanso_cuda_ctx_set_option(kanso_cuda_ctx* ctx, int32_t option, int32_t value) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "ctx_set_option: ctx is NULL");
+  switch (option) {
+    case KANSO_OPT_OVERLAP_WEIGHT_PREFETCH:
+      ctx->overlap_weight_prefetch = value != 0;
+      return KANSO_OK;
+    default:
+      return fail(ctx, KANSO_ERR_CONFIG, "ctx_set_option: unknown option %d", option);
+  }
+}
+
 uint64_t kanso_cuda_launch_count(const kanso_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
 int32_t kanso_cuda_sm_count(const kanso_cuda_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 

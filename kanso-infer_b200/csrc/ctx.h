@@ -14,6 +14,9 @@ struct kanso_cuda_ctx {
   int smem_optin = 0;      // max dynamic shared memory per block (opt-in), bytes
   int* dev_status = nullptr;  // one int on the device, OR of kanso::DevStatus
   uint64_t launches = 0;
+  // weight buffers are never written by work enqueued before a matmul on this stream, so a
+  // matmul may start fetching weights while the kernel before it is still running
+  bool overlap_weight_prefetch = false;
   std::string last_error;
   // Scratch owned by the context (split-KV partials, staged activations). Grows on demand.
   void* scratch = nullptr;

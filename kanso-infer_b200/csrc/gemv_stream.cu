@@ -515,18 +515,23 @@ int32_t stream_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const f
 
 using namespace kanso;
 
+namespace kanso {
+int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
+                        float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode);
+}
+
 extern "C" {
 
 int32_t kanso_cuda_gemv_q8_0(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
                              int64_t rows, int64_t cols) {
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "gemv_q8_0: ctx is NULL");
-  return stream_matmul(ctx, KANSO_DTYPE_Q8_0, w, x, y, 1, rows, cols, KANSO_ACT_F32);
+  return matmul_dispatch(ctx, KANSO_DTYPE_Q8_0, w, x, y, 1, rows, cols, KANSO_ACT_F32);
 }
 
 int32_t kanso_cuda_gemv_q4_k(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
                              int64_t rows, int64_t cols) {
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "gemv_q4_k: ctx is NULL");
-  return stream_matmul(ctx, KANSO_DTYPE_Q4_K, w, x, y, 1, rows, cols, KANSO_ACT_F32);
+  return matmul_dispatch(ctx, KANSO_DTYPE_Q4_K, w, x, y, 1, rows, cols, KANSO_ACT_F32);
 }
 
 }  // extern "C"

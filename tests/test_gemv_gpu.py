@@ -160,3 +160,36 @@ def test_weight_handle_and_host_linear(ctx, kb, oracle, torch_cuda):
         kb.Weight(ctx, blocks, kb.DTYPE_Q4_K, N, K)  # 960 % 256 != 0: a block may not straddle a row
     assert e.value.code == kb.ERR_SHAPE
     W.free()
+
+
+def test_overlapped_weight_prefetch_gives_same_results(kb, oracle, torch_cuda):
+    """With KANSO_OPT_OVERLAP_WEIGHT_PREFETCH consecutive GEMVs may overlap their weight
+    fetch with the kernel before them; a chain y1 = W1 x, y2 = W2 y1' must be unchanged."""
+    torch = torch_cuda
+    stream = torch.cuda.current_stream()
+    c2 = kb.Context(0, stream)
+    c2.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 1)
+    rng = np.random.Generator(np.random.PCG64(0xB2000600))
+    N1, K1, N2 = 2048, 1024, 512
+    w1 = oracle.quantize_weights_q4_k((rng.standard_normal((N1, K1)) * 0.02).astype(np.float32))
+    w2 = oracle.quantize_weights_q4_k((rng.standard_normal((N2, N1)) * 0.02).astype(np.float32))
+    x = rng.standard_normal(K1).astype(np.float32)
+    W1 = kb.Weight(c2, w1, kb.DTYPE_Q4_K, N1, K1)
+    W2 = kb.Weight(c2, w2, kb.DTYPE_Q4_K, N2, N1)
+    xd = torch.from_numpy(x).cuda()
+    y1 = torch.empty(N1, dtype=torch.float32, device="cuda")
+    y2 = torch.empty(N2, dtype=torch.float32, device="cuda")
+    for _ in range(20):  # back to back: the second kernel reads what the first one writes
+        W1.forward(xd, y1, 1)
+        W2.forward(y1, y2, 1)
+    c2.sync()
+    r1 = oracle.gemv_q4_k(w1, x, N1, K1)
+    assert rel_err(y1.cpu().numpy(), r1) <= TOL
+    r2 = oracle.gemv_q4_k(w2, y1.cpu().numpy(), N2, N1)
+    assert rel_err(y2.cpu().numpy(), r2) <= TOL
+    with pytest.raises(kb.KansoError) as e:
+        c2.set_option(99, 1)
+    assert e.value.code == kb.ERR_CONFIG
+    W1.free()
+    W2.free()
+    c2.close()
