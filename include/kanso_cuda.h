@@ -232,6 +232,29 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
                                    const uint32_t* context_lens, float* out,
                                    const kanso_paged_attention_params* params,
                                    const uint32_t* host_context_lens);
+/* The same decode attention for callers that cannot allocate device memory. It has no
+ * counterpart in the reference. kanso_cuda_paged_attention keeps its split-context partials
+ * in context scratch that grows with cudaMalloc when a larger batch arrives; an engine whose
+ * device memory is fully planned at start-up, or a caller for whom cudaMalloc's device-wide
+ * synchronisation is unacceptable (a latency-critical loop, a thread holding a lock that other
+ * GPU work waits on), uses this entry point instead: the partials live in an 8 MiB array built
+ * into the library image (every GPU that loads the library holds it until the process exits)
+ * and the call performs no cudaMalloc, cudaFree or other allocating call.
+ *   - Arguments, checks and results are those of kanso_cuda_paged_attention.
+ *   - A batch whose partials (num_seqs * num_heads * partitions * (head_dim + 2) floats) exceed
+ *     8 MiB is refused with KANSO_ERR_UNSUPPORTED; the message gives the size needed.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents
+ *     (nothing in it needs clearing: every cell read was written by the same call). Two calls
+ *     whose kernels overlap on the GPU (different streams or contexts) would race on it:
+ *     keep them on one stream or order them yourself. */
+int32_t kanso_cuda_paged_attention_noalloc(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
+                                           uint32_t layer, const float* q,
+                                           const uint32_t* block_tables,
+                                           const uint32_t* context_lens, float* out,
+                                           const kanso_paged_attention_params* params,
+                                           const uint32_t* host_context_lens);
 /* validate_paged_attention_params — src/metal/paged_attention.rs:39-81 (no device work). */
 int32_t kanso_cuda_validate_paged_attention_params(const kanso_paged_attention_params* params,
                                                    char* msg, size_t msg_len);

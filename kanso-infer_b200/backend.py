@@ -85,6 +85,8 @@ PROTOTYPES = {
     "kanso_cuda_kv_bytes_per_token": (_U64, [_P]),
     "kanso_cuda_paged_attention": (_I32, [_P, _P, _U32, _P, _P, _P, _P,
                                           C.POINTER(PagedAttentionParams), _P]),
+    "kanso_cuda_paged_attention_noalloc": (_I32, [_P, _P, _U32, _P, _P, _P, _P,
+                                                  C.POINTER(PagedAttentionParams), _P]),
     "kanso_cuda_validate_paged_attention_params": (_I32, [C.POINTER(PagedAttentionParams),
                                                           C.c_char_p, _SZ]),
     "kanso_cuda_rmsnorm": (_I32, [_P, _P, _P, _P, _I64, _I64, _F]),
@@ -309,6 +311,14 @@ class KvPool:
                         params: PagedAttentionParams, host_context_lens=None):
         self.ctx.call("kanso_cuda_paged_attention", self.h, layer, _ptr(q), _ptr(block_tables),
                       _ptr(context_lens), _ptr(out), C.byref(params), _ptr(host_context_lens))
+
+
+    def paged_attention_noalloc(self, layer, q, block_tables, context_lens, out,
+                                params: PagedAttentionParams, host_context_lens=None):
+        """Same call with the partials in the library's built-in array (no allocation)."""
+        self.ctx.call("kanso_cuda_paged_attention_noalloc", self.h, layer, _ptr(q),
+                      _ptr(block_tables), _ptr(context_lens), _ptr(out), C.byref(params),
+                      _ptr(host_context_lens))
 
 
 def validate_paged_attention_params(params: PagedAttentionParams):

@@ -397,3 +397,165 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// An engine that plans all of its device memory up front (the KV pool is sized from a memory
+// budget when the engine starts, and nothing may grow afterwards), or that calls from a place
+// where cudaMalloc is off limits because it synchronises the whole device (a latency-critical
+// serving loop, a thread that holds a lock other GPU work waits on), cannot use the entry
+// point above: its split-context partials live in context scratch that grows on demand. This
+// variant keeps the partials in a fixed array that is part of the loaded library image, so the
+// call itself performs no allocation of any kind.
+namespace kanso {
+
+// Every GPU that loads the library carries this array until the process exits.
+constexpr size_t PA_STATIC_SCRATCH_BYTES = size_t(8) << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_pa_static_scratch[PA_STATIC_SCRATCH_BYTES];
+
+// Device address of the array, looked up once per device. In host code the symbol's name is
+// only a handle for the runtime, not a device pointer, so it must never be handed to a kernel
+// directly; cudaGetSymbolAddress translates it for the device that is current.
+static unsigned char* pa_static_scratch_ptr(kanso_cuda_ctx* ctx, int32_t* status) {
+  static unsigned char* per_device[64] = {nullptr};
+  *status = KANSO_OK;
+  const int dev = ctx->device;
+  if (dev < 0 || dev >= 64) {
+    *status = fail(ctx, KANSO_ERR_UNSUPPORTED, "paged_attention_noalloc: device index %d", dev);
+    return nullptr;
+  }
+  if (!per_device[dev]) {
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e == cudaSuccess && cur != dev) e = cudaSetDevice(dev);
+    unsigned char* p = nullptr;
+    if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&p, g_pa_static_scratch);
+    if (e != cudaSuccess || !p) {
+      *status = cuda_fail(ctx, e, "paged_attention_noalloc: cudaGetSymbolAddress");
+      return nullptr;
+    }
+    per_device[dev] = p;
+  }
+  return per_device[dev];
+}
+
+static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
+                                             uint32_t layer, const float* q,
+                                             const uint32_t* tables, const uint32_t* lens,
+                                             float* out, const kanso_paged_attention_params* p,
+                                             uint32_t max_ctx_hint) {
+  KvGeom g = kv_geom(kv);
+  const uint32_t G = p->num_heads / p->num_kv_heads;
+  const uint32_t hd = p->head_dim;
+  uint64_t cap = (uint64_t)p->max_num_blocks_per_seq * p->block_size;
+  if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
+  uint32_t pt = 512;
+  while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
+                        2ull * ctx->sm_count)
+    pt >>= 1;
+  if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
+  const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
+
+  const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
+  const size_t acc_bytes = nheads_total * nparts * hd * sizeof(float);
+  const size_t acc_al = (acc_bytes + 255) & ~size_t(255);
+  const size_t ml_bytes = nheads_total * nparts * 2 * sizeof(float);
+  if (acc_al + ml_bytes > PA_STATIC_SCRATCH_BYTES)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                "paged_attention_noalloc: this batch needs %zu bytes of partials (%u sequences x "
+                "%u heads x %u partitions x head_dim %u); the built-in scratch holds %zu. Split "
+                "the batch or use kanso_cuda_paged_attention",
+                acc_al + ml_bytes, p->num_seqs, p->num_heads, nparts, hd,
+                (size_t)PA_STATIC_SCRATCH_BYTES);
+  int32_t st;
+  unsigned char* scratch = pa_static_scratch_ptr(ctx, &st);
+  if (!scratch) return st;
+
+  PaArgs a;
+  a.g = g;
+  a.layer = layer;
+  a.q = q;
+  a.tables = tables;
+  a.lens = lens;
+  a.out = out;
+  // Nothing in the array has to start at zero: stage 1 writes every partition that stage 2
+  // reads for a sequence (those below its context length), so stale contents are never used.
+  a.part_acc = reinterpret_cast<float*>(scratch);
+  a.part_ml = reinterpret_cast<float*>(scratch + acc_al);
+  a.num_heads = p->num_heads;
+  a.max_blocks = p->max_num_blocks_per_seq;
+  a.part_tokens = pt;
+  a.num_parts = nparts;
+  a.scale = p->scale;
+  a.status = ctx->dev_status;
+
+  const uint32_t nblk_part = ((pt + p->block_size - 1) / p->block_size + 4) & ~3u;
+  const uint32_t words = hd / 4, nslice = PA_THREADS / words;
+  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4;
+  size_t red_bytes = (size_t)nslice * G * hd * 4;
+  if (red_bytes < 128) red_bytes = 128;
+  smem += red_bytes;
+  if (smem > (size_t)ctx->smem_optin)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                "paged_attention_noalloc: %zu bytes of shared memory needed", smem);
+  dim3 grid(nparts, p->num_kv_heads, p->num_seqs);
+  switch (G) {
+    case 1: launch_stage1<1>(a, grid, smem, ctx->stream); break;
+    case 2: launch_stage1<2>(a, grid, smem, ctx->stream); break;
+    case 3: launch_stage1<3>(a, grid, smem, ctx->stream); break;
+    case 4: launch_stage1<4>(a, grid, smem, ctx->stream); break;
+    case 5: launch_stage1<5>(a, grid, smem, ctx->stream); break;
+    case 6: launch_stage1<6>(a, grid, smem, ctx->stream); break;
+    case 7: launch_stage1<7>(a, grid, smem, ctx->stream); break;
+    default: launch_stage1<8>(a, grid, smem, ctx->stream); break;
+  }
+  st = after_launch(ctx, "paged_attention_noalloc stage 1");
+  if (st) return st;
+  paged_attn_stage2<<<dim3(p->num_heads, p->num_seqs), 64, 0, ctx->stream>>>(a);
+  return after_launch(ctx, "paged_attention_noalloc stage 2");
+}
+
+}  // namespace kanso
+
+extern "C" int32_t kanso_cuda_paged_attention_noalloc(
+    kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer, const float* q,
+    const uint32_t* block_tables, const uint32_t* context_lens, float* out,
+    const kanso_paged_attention_params* params, const uint32_t* host_context_lens) {
+  if (!ctx) return kanso::fail(nullptr, KANSO_ERR_CONFIG, "paged_attention_noalloc: ctx is NULL");
+  char msg[256];
+  int32_t st = kanso::validate_params(params, msg, sizeof msg);
+  if (st) return kanso::fail(ctx, st, "%s", msg);
+  if (!kv || !q || !block_tables || !context_lens || !out)
+    return kanso::fail(ctx, KANSO_ERR_SHAPE, "paged_attention_noalloc: NULL pointer");
+  if (layer >= kv->layers)
+    return kanso::fail(ctx, KANSO_ERR_SHAPE, "Layer index %u out of bounds (%u)", layer,
+                       kv->layers);
+  if (params->num_kv_heads != kv->kv_heads || params->head_dim != kv->head_dim ||
+      params->block_size != kv->block_size)
+    return kanso::fail(ctx, KANSO_ERR_SHAPE,
+                       "paged attention: params (kv_heads %u, head_dim %u, block_size %u) do not "
+                       "match the pool (%u, %u, %u)",
+                       params->num_kv_heads, params->head_dim, params->block_size, kv->kv_heads,
+                       kv->head_dim, kv->block_size);
+  const uint32_t hd = params->head_dim;
+  if (hd < 16 || (hd & (hd - 1)) != 0)
+    return kanso::fail(ctx, KANSO_ERR_UNSUPPORTED,
+                       "paged attention: head_dim %u is not one of 16, 32, 64, 128, 256", hd);
+  uint32_t max_ctx = 0;
+  if (host_context_lens) {
+    const uint64_t cap = (uint64_t)params->max_num_blocks_per_seq * params->block_size;
+    for (uint32_t s = 0; s < params->num_seqs; ++s) {
+      if (host_context_lens[s] == 0)
+        return kanso::fail(ctx, KANSO_ERR_UNSUPPORTED,
+                           "paged attention: sequence %u has context 0", s);
+      if (host_context_lens[s] > cap)
+        return kanso::fail(ctx, KANSO_ERR_UNSUPPORTED,
+                           "paged attention: sequence %u context %u exceeds table capacity %llu",
+                           s, host_context_lens[s], (unsigned long long)cap);
+      if (host_context_lens[s] > max_ctx) max_ctx = host_context_lens[s];
+    }
+  }
+  return kanso::launch_paged_attention_static(ctx, kv, layer, q, block_tables, context_lens, out,
+                                              params, max_ctx);
+}
