@@ -33,6 +33,7 @@ UP = (14336, 4096)    # rows (N), cols (K)
 DOWN = (4096, 14336)
 Q4K_BYTES, QK_K = 144, 256
 SEED = 0xB2000000 + 2 * 100
+NCU_DRAM_BYTES_PER_LAUNCH = 33_067_776
 
 
 def alg_bytes(rows, cols):
@@ -316,10 +317,9 @@ def run_ours(args):
         peak, peak_src = 6650.0, "fallback"
     per_launch_bytes = (alg_bytes(*UP) + alg_bytes(*DOWN)) / 2
     achieved = per_launch_bytes / (us_per_launch * 1e-6) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "gemv_stream_q4_k_cfg2.traffic.json")
-    if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+    # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
+    # profiles/gemv_q4k_mma_cfg2.md (a profiler figure: it is not re-measured by this run)
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH
 
     cpu = cpu_baseline_1core(O, up0, down0, [x_up, x_down]) if (world == 1 and not os.environ.get("KANSO_BENCH_SKIP_CPU")) else None
     line = {
@@ -335,7 +335,7 @@ def run_ours(args):
                    "check_vs_oracle_rel_err": err},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
-                     "kernel": "gemv_stream_kernel<Q4_K>", "us_per_launch": us_per_launch,
+                     "kernel": "gemv_q4k_mma_kernel", "us_per_launch": us_per_launch,
                      "alg_bytes_per_launch": per_launch_bytes},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
     }
