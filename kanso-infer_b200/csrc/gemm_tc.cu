@@ -1,0 +1,387 @@
+// Batched quantized GEMM on the 5th-generation tensor cores (tcgen05 + TMEM):
+// LinearWeight::forward for many activation rows (src/weights.rs:43-45; continuous-batching
+// and chunked-prefill rows of forward_batch_rows, src/model.rs:1418-1740).
+//
+//   y[M,N] = x[M,K] @ W[N,K]^T,  W in GGUF Q8_0 / Q4_K blocks, x and y f32.
+//
+// Mapping. The weight matrix is the 128-row operand of the MMA (A, K-major) and the
+// activations are the narrow operand (B, K-major, 16..256 rows), so one CTA owns 128 weight
+// rows x one K range and streams its weight bytes from HBM exactly once:
+//   * a small pre-pass converts x to f16 in the canonical K-major core-matrix layout, one
+//     contiguous tile per 64-wide K stage, so every CTA fetches its B tiles with plain
+//     128-bit copies out of L2;
+//   * per stage (64 values of K) the CTA's warps read the quantized blocks of its 128 rows
+//     straight from global memory, dequantise in registers (Q8_0: exact int8 -> f16 by byte
+//     permute, one rounding in d*q; Q4_K: (d*sc)*q - dmin*m in f32, one rounding to f16) and
+//     store 16-byte core-matrix rows into shared memory (no swizzle: 8 rows x 16 bytes per
+//     core matrix, K-adjacent matrices 2 KB apart), double-buffered;
+//   * one elected thread issues four tcgen05.mma (M=128, N=Mt, K=16, kind::f16, f32
+//     accumulate in TMEM) per stage and commits them to an mbarrier, which frees the stage;
+//   * after the last stage four warps read the accumulator with tcgen05.ld (lane = weight
+//     row, column = activation row) and write y; with split-K the partial sums are added
+//     with red.global (y is cleared first).
+// Every mbarrier wait is bounded; on a timeout the CTA records DEV_WAIT_TIMEOUT, frees its
+// TMEM columns and returns.
+//
+// Numerics: both operands are rounded once to f16 (relative 2^-12 on average) and products
+// accumulate in f32; against the f32 reference this gives ~2-4e-4 of the output scale, inside
+// the 1e-3 bound. KANSO_ACT_Q8 (bit-exact int32 block sums) is not offered on this path: its
+// per-32 scales would force the accumulator out of TMEM every K=32.
+#include "ctx.h"
+
+namespace kanso {
+
+constexpr int TC_THREADS = 256;
+constexpr int TC_KC = 64;        // K values per stage
+constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
+constexpr int TC_A_STAGE = TC_TILE_N * TC_KC * 2;  // bytes of f16 A per stage (16 KB)
+
+struct TcArgs {
+  const uint8_t* w;
+  const __half* xp;  // packed activations [K/64][8][Mt][8]
+  float* y;
+  int64_t N;
+  int K, M, Mt;      // Mt = M rounded up to 16
+  int bpr;           // blocks (Q8_0) or super-blocks (Q4_K) per row
+  int ksplit;        // CTAs along K
+  int stages_total;  // K / 64
+  int* status;
+};
+
+// x f32 [M,K] -> f16, layout [stage][chunk of 8 k][row m][8 values]; rows >= M are zero.
+// perm: order of the values inside a chunk (Q4_K's nibble unpack yields k order 0,2,1,3,...).
+__global__ void tc_pack_activations_kernel(const float* __restrict__ x, __half* __restrict__ xp,
+                                           int M, int Mt, int K, int perm) {
+  const int64_t total = (int64_t)(K / 8) * Mt;  // one thread per (chunk, row)
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i % Mt);
+    const int chunk = (int)(i / Mt);  // global chunk index = k / 8
+    __align__(16) __half v[8];
+    if (m < M) {
+      const float4* src = reinterpret_cast<const float4*>(x + (int64_t)m * K + chunk * 8);
+      const float4 a = __ldg(src), b = __ldg(src + 1);
+      const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // perm: position p holds k = {0,2,1,3,4,6,5,7}[p]
+        const int k = perm ? ((j & 4) | ((j & 1) << 1) | ((j >> 1) & 1)) : j;
+        v[j] = __float2half_rn(f[k]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(0.f);
+    }
+    // [stage][chunk in stage][m][8]  ==  [chunk][m][8] since a stage is 8 consecutive chunks
+    *reinterpret_cast<uint4*>(xp + ((int64_t)chunk * Mt + m) * 8) = *reinterpret_cast<uint4*>(v);
+  }
+}
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns of this warp's TMEM quarter
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+      "%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored
+// contiguously; lbo = bytes between core matrices adjacent in K, sbo = bytes between core
+// matrices adjacent in the row (M/N) direction.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  return d;                // base offset 0, swizzle mode 0 (none)
+}
+// Instruction descriptor for kind::f16: f16 x f16 -> f32, both operands K-major.
+__host__ __device__ inline uint32_t tc_idesc_f16(int m, int n) {
+  uint32_t d = 0;
+  d |= 1u << 4;                      // accumulator format f32
+  d |= 0u << 7;                      // A format f16
+  d |= 0u << 10;                     // B format f16
+  d |= (uint32_t)(n >> 3) << 17;     // N / 8
+  d |= (uint32_t)(m >> 4) << 24;     // M / 16
+  return d;
+}
+
+constexpr int TC_FMT_Q8_0 = 0;
+constexpr int TC_FMT_Q4_K = 1;
+
+// Dequantise this thread's 32 weights of stage `s` into the A tile (core-matrix layout).
+// Q8_0: thread = (block tid / 128 of the two in the stage, row tid % 128).
+__device__ __forceinline__ void tc_dequant_q8_0(const TcArgs& a, int64_t n, int s, int tid,
+                                                uint8_t* As) {
+  const int blk = tid >> 7, row = tid & 127;
+  const uint8_t* p = a.w + (n * a.bpr + (int64_t)s * 2 + blk) * Q8_BYTES;
+  // the block is only 2-byte aligned: read the nine aligned words that cover it
+  const uintptr_t pa = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* al = reinterpret_cast<const uint32_t*>(pa & ~uintptr_t(3));
+  const uint32_t sh = (uint32_t)(pa & 3) * 8;  // 0 or 16
+  uint32_t r[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) r[k] = __ldg(al + k);
+  uint32_t v[9];  // the 34 bytes of the block, from its first byte
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = __funnelshift_r(r[k], r[k + 1], sh);
+  v[8] = r[8] >> sh;
+  const __half d = __ushort_as_half((unsigned short)(v[0] & 0xFFFFu));
+  const __half2 d2 = __half2half2(d);
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128, exact in f16
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {  // chunk of 8 weights = two words of int8
+    uint32_t out[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t q = __funnelshift_r(v[2 * c + h], v[2 * c + h + 1], 16) ^ 0x80808080u;
+      // 0x6400 | byte = 1024 + (q + 128) as f16, exactly
+      uint32_t p01 = __byte_perm(q, 0x64646464u, 0x4140);
+      uint32_t p23 = __byte_perm(q, 0x64646464u, 0x4342);
+      __half2 h01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), bias), d2);
+      __half2 h23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), bias), d2);
+      out[2 * h] = *reinterpret_cast<uint32_t*>(&h01);
+      out[2 * h + 1] = *reinterpret_cast<uint32_t*>(&h23);
+    }
+    const int kc = blk * 4 + c;  // chunk of 8 k-values within the stage
+    *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
+        make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+// Q4_K: stage s = 64-weight group g = s % 4 of super-block s / 4; thread = (nibble half
+// tid / 128 -> sub-block 2g + half, row tid % 128). (d*sc)*q - dmin*m as src/quant/q4_k.rs:30-55,
+// then one rounding to f16.
+__device__ __forceinline__ void tc_dequant_q4_k(const TcArgs& a, int64_t n, int s, int tid,
+                                                uint8_t* As) {
+  const int half = tid >> 7, row = tid & 127;
+  const int sb = s >> 2, g = s & 3;
+  const uint8_t* p = a.w + (n * a.bpr + sb) * Q4K_BYTES;
+  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 qa = __ldg(reinterpret_cast<const uint4*>(p + 16 + 32 * g));
+  const uint4 qb = __ldg(reinterpret_cast<const uint4*>(p + 32 + 32 * g));
+  const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+  uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+  unpack_scales_k4(hdr.y, hdr.z, hdr.w, sc_lo, sc_hi, mn_lo, mn_hi);
+  const int j = 2 * g + half;
+  const uint32_t scw = j < 4 ? sc_lo : sc_hi, mnw = j < 4 ? mn_lo : mn_hi;
+  const float d1 = __fmul_rn(d, (float)((scw >> (8 * (j & 3))) & 0xFF));
+  const float m1 = __fmul_rn(dmin, (float)((mnw >> (8 * (j & 3))) & 0xFF));
+  const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+  const int sh0 = 4 * half;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t out[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t w = qw[2 * c + h] >> sh0;
+      float f[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float q = __uint_as_float(0x4B000000u | ((w >> (8 * b)) & 0xFu)) - 8388608.0f;
+        f[b] = __fsub_rn(__fmul_rn(d1, q), m1);
+      }
+      __half2 h01 = __floats2half2_rn(f[0], f[1]);
+      __half2 h23 = __floats2half2_rn(f[2], f[3]);
+      out[2 * h] = *reinterpret_cast<uint32_t*>(&h01);
+      out[2 * h + 1] = *reinterpret_cast<uint32_t*>(&h23);
+    }
+    const int kc = half * 4 + c;  // low nibbles: k 0..31 of the group, high nibbles: 32..63
+    *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
+        make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t b_stage = 8u * a.Mt * 16u;  // bytes of the B tile of one stage
+  uint8_t* As = smem;
+  uint8_t* Bs = smem + 2 * TC_A_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Bs + 2 * b_stage);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+
+  const int64_t n0 = (int64_t)blockIdx.x * TC_TILE_N;
+  const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
+  const int s1 = (int)((int64_t)a.stages_total * (blockIdx.y + 1) / a.ksplit);
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)a.Mt) ncols <<= 1;
+
+  if (warp == 0) tmem_alloc(tmem_slot, ncols);
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_fence_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
+
+  const int64_t n_row = min(n0 + (tid & 127), a.N - 1);  // rows past N re-read the last row
+  int failed = 0;
+  for (int s = s0; s < s1; ++s) {
+    const int it = s - s0, buf = it & 1;
+    if (it >= 2)  // the MMAs that read this buffer two stages ago must be done
+      failed = !mbar_wait_bounded(&bars[buf], (uint32_t)((it - 2) >> 1) & 1);
+    if (__syncthreads_or(failed)) {
+      failed = 1;
+      break;
+    }
+    uint8_t* Ab = As + buf * TC_A_STAGE;
+    uint8_t* Bb = Bs + buf * b_stage;
+    if (FMT == TC_FMT_Q8_0)
+      tc_dequant_q8_0(a, n_row, s, tid, Ab);
+    else
+      tc_dequant_q4_k(a, n_row, s, tid, Ab);
+    const uint4* bsrc = reinterpret_cast<const uint4*>(a.xp) + (size_t)s * (b_stage / 16);
+    for (uint32_t i = tid; i < b_stage / 16; i += TC_THREADS)
+      reinterpret_cast<uint4*>(Bb)[i] = __ldg(bsrc + i);
+    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(Ab), b_addr = smem_u32(Bb);
+#pragma unroll
+      for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
+        const uint64_t ad = tc_smem_desc(a_addr + j * 2 * (TC_TILE_N * 16), TC_TILE_N * 16, 128);
+        const uint64_t bd = tc_smem_desc(b_addr + j * 2 * (a.Mt * 16), a.Mt * 16, 128);
+        tc_mma_f16(tmem_base, ad, bd, idesc, (it > 0 || j > 0) ? 1u : 0u);
+      }
+      tc_commit(&bars[buf]);
+    }
+  }
+  if (!failed && s1 > s0) {
+    const int last = s1 - s0 - 1;
+    failed = !mbar_wait_bounded(&bars[last & 1], (uint32_t)(last >> 1) & 1);
+  }
+  failed = __syncthreads_or(failed);
+  tc_fence_after();
+  if (!failed && s1 > s0) {
+    // lane = weight row inside the tile, column = activation row
+    const int q = warp & 3;
+    const int64_t n = n0 + q * 32 + lane;
+    for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += 2) {
+      uint32_t r[16];
+      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
+      if (n < a.N) {
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          const int m = c16 * 16 + jj;
+          if (m < a.M) {
+            float* dst = a.y + (int64_t)m * a.N + n;
+            if (a.ksplit == 1)
+              *dst = __uint_as_float(r[jj]);
+            else
+              atomicAdd(dst, __uint_as_float(r[jj]));
+          }
+        }
+      }
+    }
+  } else if (failed && tid == 0) {
+    atomicOr(a.status, DEV_WAIT_TIMEOUT);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, ncols);
+}
+
+// y[M,N] = x[M,K] @ W^T on the tensor cores; M in 9..256 per call (larger M is chunked by
+// the caller). Sets *handled = false when the shape is outside this kernel's range.
+int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
+                  int64_t M, int64_t N, int64_t K, bool* handled) {
+  *handled = false;
+  const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
+  if (M < 1 || M > 256 || N < 1 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
+  if (dtype == KANSO_DTYPE_Q8_0 && (reinterpret_cast<uintptr_t>(w) & 3) != 0) return KANSO_OK;
+  const int Mt = (int)((M + 15) / 16 * 16);
+  const int stages_total = (int)(K / TC_KC);
+  const int tiles_n = (int)((N + TC_TILE_N - 1) / TC_TILE_N);
+  // split K until the grid covers the SMs about twice, keeping >= 4 stages per CTA
+  int ksplit = 1;
+  while (tiles_n * ksplit < 2 * ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
+  const size_t xp_bytes = (size_t)(K / 8) * Mt * 16;
+  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
+  if (!scratch) return KANSO_ERR_DEVICE;
+  *handled = true;
+
+  const int64_t chunks = (K / 8) * Mt;
+  tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
+      x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, 0);
+  int32_t st = after_launch(ctx, "gemm_tc pack activations");
+  if (st) return st;
+  if (ksplit > 1)
+    KANSO_CUDA_TRY(ctx, cudaMemsetAsync(y, 0, sizeof(float) * (size_t)M * N, ctx->stream),
+                   "gemm_tc: clear y");
+
+  TcArgs a;
+  a.w = (const uint8_t*)w;
+  a.xp = reinterpret_cast<const __half*>(scratch);
+  a.y = y;
+  a.N = N;
+  a.K = (int)K;
+  a.M = (int)M;
+  a.Mt = Mt;
+  a.bpr = (int)(K / blk);
+  a.ksplit = ksplit;
+  a.stages_total = stages_total;
+  a.status = ctx->dev_status;
+  const size_t smem = 2 * TC_A_STAGE + 2 * (size_t)(8 * Mt * 16) + 64;
+  auto kern = dtype == KANSO_DTYPE_Q8_0 ? gemm_tc_kernel<TC_FMT_Q8_0> : gemm_tc_kernel<TC_FMT_Q4_K>;
+  static bool attr_set[2][16] = {};
+  bool& done = attr_set[dtype == KANSO_DTYPE_Q8_0 ? 0 : 1][ctx->device & 15];
+  if (!done) {
+    KANSO_CUDA_TRY(ctx,
+                   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ctx->smem_optin),
+                   "gemm_tc: shared memory opt-in");
+    done = true;
+  }
+  kern<<<dim3(tiles_n, ksplit), TC_THREADS, smem, ctx->stream>>>(a);
+  return after_launch(ctx, "gemm_tc");
+}
+
+}  // namespace kanso
