@@ -215,30 +215,62 @@ def run_ours(args):
     x_up = rng.standard_normal(UP[1]).astype(np.float32)
     x_down = rng.standard_normal(DOWN[1]).astype(np.float32)
 
-    W_up = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *UP) for b in ups]
-    W_down = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *DOWN) for b in downs]
     dx_up = torch.from_numpy(x_up).cuda()
     dx_down = torch.from_numpy(x_down).cuda()
     y_up = torch.empty(UP[0], dtype=torch.float32, device="cuda")
     y_down = torch.empty(DOWN[0], dtype=torch.float32, device="cuda")
+    if world == 1:
+        W_up = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *UP) for b in ups]
+        W_down = [kb.Weight(ctx, b, kb.DTYPE_Q4_K, *DOWN) for b in downs]
 
-    def step():
-        for wu, wd in zip(W_up, W_down):
-            wu.forward(dx_up, y_up, 1)
-            wd.forward(dx_down, y_down, 1)
+        def step():
+            for wu, wd in zip(W_up, W_down):
+                wu.forward(dx_up, y_up, 1)
+                wd.forward(dx_down, y_down, 1)
+    else:
+        # Weak scaling of the sharded layer pair: every rank keeps config 2's shard sizes.
+        # W_up[world*14336 x 4096] is split by output rows, its y gathered by the GEMV kernel's
+        # own peer stores; W_down[4096 x world*14336] is split along K and all-reduced (NCCL).
+        sh = importlib.import_module("kanso-infer_b200").sharded
+        S_up = [sh.RowShardedLinear(ctx, b, kb.DTYPE_Q4_K, world * UP[0], UP[1], mode="fused",
+                                    max_m=1, presharded=True) for b in ups]
+        S_down = [sh.KShardedLinear(ctx, b, kb.DTYPE_Q4_K, DOWN[0], world * DOWN[1], max_m=1,
+                                    presharded=True) for b in downs]
+        W_up = [s.weight for s in S_up]
+        W_down = [s.weight for s in S_down]
+        dx_up2 = dx_up.reshape(1, -1)
+        dx_down2 = dx_down.reshape(1, -1)
+
+        def step():
+            for su, sd in zip(S_up, S_down):
+                y_up_full = su.forward(dx_up2, 1)
+                y_dn = sd.forward(dx_down2, 1)
+            y_up.copy_(y_up_full[0, su.row_begin:su.row_begin + su.row_count])
+            y_down.copy_(y_dn[0])
 
     # result check against the oracle on the last pair (not timed)
     step()
     ctx.sync()
-    ref_up = O.gemv_q4_k(ups[-1], x_up, *UP)
+    ref_up = O.gemv_q4_k(ups[-1], x_up, *UP)  # at N > 1: this rank's slice of the gathered y
     err = float(np.max(np.abs(y_up.cpu().numpy() - ref_up)) / np.max(np.abs(ref_up)))
     if err > 1e-3:
         raise SystemExit(f"bench: GEMV result differs from the oracle by {err:.2e} (> 1e-3)")
 
     launches_per_step = 2 * pairs
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        step()
+
+    class _Eager:  # same interface as a captured graph, for steps that cannot be captured
+        def replay(self):
+            step()
+
+    if world == 1:
+        launch_mode = "CUDA graph of the step"
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    else:
+        # the collectives (NCCL all-reduce, symmetric-memory barrier) are launched step by
+        # step: a capture of them stalled in a 2-GPU trial, so they stay out of a graph
+        graph, launch_mode = _Eager(), "eager launches (collectives are not captured)"
     for _ in range(max(3, args.warmup)):
         graph.replay()
     torch.cuda.synchronize()
@@ -265,11 +297,15 @@ def run_ours(args):
         ms = float(t.item())
     # keep sampling for a moment so that short timed regions still get samples
     clocks = None
-    if rank == 0:
+    if world == 1:
         t_end = time.time() + 1.0
         while time.time() < t_end:
             graph.replay()
-        torch.cuda.synchronize()
+    else:  # every rank must take part in the collectives: a fixed number of extra steps
+        for _ in range(200):
+            graph.replay()
+    torch.cuda.synchronize()
+    if rank == 0:
         clocks = sampler.stop()
 
     step_bytes = pairs * (alg_bytes(*UP) + alg_bytes(*DOWN))
@@ -331,7 +367,7 @@ def run_ours(args):
                    "ring_pairs": pairs, "bytes_per_step": step_bytes,
                    "l2": f"inputs larger than L2: {step_bytes / 1e6:.0f} MB of distinct weights "
                          "per step vs 126 MB L2",
-                   "launch": "CUDA graph of the step", "parallelism": f"shards{world}",
+                   "launch": launch_mode, "parallelism": (f"shards{world}" if world == 1 else f"row-shard all-gather (fused peer stores) + K-shard all-reduce (NCCL) over {world} GPUs"),
                    "check_vs_oracle_rel_err": err},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,

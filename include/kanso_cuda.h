@@ -183,6 +183,28 @@ int32_t kanso_cuda_linear_host(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
 /* Same with device activations, asynchronous. */
 int32_t kanso_cuda_linear(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const float* x,
                           float* y, int64_t M, int32_t act_mode);
+/* ---- sharding one linear layer over the GPUs of a node (one process per GPU). The reference
+ * has no multi-GPU path (docs/SPEC.md:125); these extend LinearWeight::to_device and
+ * Model::linear (src/weights.rs:140-158, src/model.rs:390-397). ---- */
+/* The part of [0, n) that rank `rank` of `world` owns, in multiples of `align`
+ * (8 rows for output-row sharding, the block size for K sharding). Host only. */
+int32_t kanso_cuda_shard_range(int64_t n, int32_t rank, int32_t world, int64_t align,
+                               int64_t* begin, int64_t* count);
+/* K sharding: copies the blocks of columns [col_begin, col_begin + col_count) of every row
+ * into a contiguous [rows x col_count] block matrix (host to host). */
+int32_t kanso_cuda_shard_k_repack(const void* host_bytes, int32_t dtype, int64_t rows,
+                                  int64_t cols, int64_t col_begin, int64_t col_count,
+                                  void* out_bytes, size_t out_capacity);
+/* Output-row sharding with the gather fused into the matmul's epilogue: w holds rows
+ * [row_offset, row_offset + w.rows) of an [n_total x cols] weight; the slice
+ * y[m, row_offset + r] is stored into every one of the n_out (<= 8) result buffers
+ * y_out[i] (f32 [M, n_total]; this GPU's own and its peers' buffers mapped into this
+ * process, e.g. symmetric memory). Stores to peers are plain stores over NVLink; the caller
+ * orders them against the readers with its usual cross-GPU barrier. */
+int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
+                                      const float* x, int64_t M, float* const* y_out,
+                                      int32_t n_out, int64_t n_total, int64_t row_offset,
+                                      int32_t act_mode);
 /* LinearWeight::embed — src/weights.rs:50-57: dequantise the selected rows.
  * ids u32[T] (device), out f32[T, cols] (device). An id >= rows -> KANSO_ERR_SHAPE
  * is reported by the device status word at the next kanso_cuda_sync. */

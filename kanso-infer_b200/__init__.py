@@ -3,6 +3,6 @@
 The product is the C-ABI shared library built from csrc/ (see include/kanso_cuda.h);
 `backend` binds it with ctypes for tests and measurement, `build` compiles it.
 """
-from . import backend, build  # noqa: F401
+from . import backend, build, sharded  # noqa: F401
 
-__all__ = ["backend", "build"]
+__all__ = ["backend", "build", "sharded"]

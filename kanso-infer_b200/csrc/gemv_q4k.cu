@@ -40,10 +40,17 @@ constexpr int Q4M_ROW_STRIDE = 160;    // bytes between the rows of an item in a
 constexpr int Q4M_SLOT = 8 * Q4M_ROW_STRIDE;
 constexpr int Q4M_PLANE_PAD = 32;  // plane stride K+32: the B loads of a warp hit distinct banks
 
+constexpr int Q4M_MAX_OUT = 8;
+
 struct Q4kArgs {
   const uint8_t* w;
   const float* x;
   float* y;
+  // row-sharded use: the CTA's rows are also stored into these result buffers (this GPU's
+  // and its peers'), at row y_row_offset + r of rows of length ldy
+  float* y_out[Q4M_MAX_OUT];
+  int n_out;
+  int64_t y_row_offset;
   int64_t rows, ldx, ldy;
   int K, bpr, M;
   int max_rows_cta;
@@ -331,7 +338,12 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
     const float* p = ypart + (size_t)m * bpr * max_rows + r;
     float acc = 0.f;
     for (int S = 0; S < bpr; ++S) acc += p[S * max_rows];
-    a.y[(int64_t)m * a.ldy + rb + r] = acc;
+    if (a.n_out == 0) {
+      a.y[(int64_t)m * a.ldy + rb + r] = acc;
+    } else {
+      for (int o = 0; o < a.n_out; ++o)  // plain stores, also into peers' memory over NVLink
+        a.y_out[o][(int64_t)m * a.ldy + a.y_row_offset + rb + r] = acc;
+    }
   }
 }
 
@@ -389,9 +401,20 @@ static Q4kCfg q4k_cfg() {
 
 // Sets *handled when this kernel took the call; leaves it false when the shape is outside
 // its range (the caller then uses the general streaming kernel).
+int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                              int64_t M, int64_t N, int64_t K, bool* handled, float* const* y_out,
+                              int n_out, int64_t ld_out, int64_t row_offset);
+
 int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y, int64_t M,
                           int64_t N, int64_t K, bool* handled) {
+  return q4k_direct_matmul_out(ctx, w, x, y, M, N, K, handled, nullptr, 0, N, 0);
+}
+
+int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                              int64_t M, int64_t N, int64_t K, bool* handled, float* const* y_out,
+                              int n_out, int64_t ld_out, int64_t row_offset) {
   *handled = false;
+  if (n_out < 0 || n_out > Q4M_MAX_OUT) return KANSO_OK;
   if (K % 256 != 0 || M < 1 || M > 8 || N < 8 || N % 8 != 0) return KANSO_OK;
   const Q4kCfg cfg = q4k_cfg();
   int grid = ctx->sm_count * cfg.cps;
@@ -405,7 +428,10 @@ int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
   a.y = y;
   a.rows = N;
   a.ldx = K;
-  a.ldy = N;
+  a.ldy = n_out ? ld_out : N;
+  a.n_out = n_out;
+  a.y_row_offset = row_offset;
+  for (int o = 0; o < Q4M_MAX_OUT; ++o) a.y_out[o] = o < n_out ? y_out[o] : nullptr;
   a.K = (int)K;
   a.bpr = (int)(K / 256);
   a.M = (int)M;

@@ -1,0 +1,115 @@
+// Sharding a quantized linear layer over the GPUs of one node. The reference has no
+// multi-GPU code (docs/SPEC.md:125); the pieces here extend LinearWeight::to_device
+// (src/weights.rs:140-158) and Model::linear (src/model.rs:390-397):
+//   * output-row sharding: rank r holds a contiguous range of weight rows; every rank
+//     produces its slice of y (an all-gather assembles the vector where it is needed);
+//   * K sharding: rank r holds the blocks of a contiguous range of columns of every row,
+//     re-packed into its own [rows x K/world] block matrix; partial results are summed.
+// Blocks never straddle a shard: ranges are multiples of the block size (and of 8 rows).
+#include <cstring>
+
+#include "ctx.h"
+
+namespace kanso {
+int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
+                        float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode);
+int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                              int64_t M, int64_t N, int64_t K, bool* handled, float* const* y_out,
+                              int n_out, int64_t ld_out, int64_t row_offset);
+
+struct ScatterArgs {
+  float* out[8];
+  int n_out;
+};
+// src f32 [M, rows] -> out[o][m * ld + row_offset + r] for every result buffer
+__global__ void scatter_rows_kernel(const float* __restrict__ src, ScatterArgs a, int64_t M,
+                                    int64_t rows, int64_t ld, int64_t row_offset) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * rows) return;
+  int64_t m = i / rows, r = i - m * rows;
+  float v = src[i];
+  for (int o = 0; o < a.n_out; ++o) a.out[o][m * ld + row_offset + r] = v;
+}
+}  // namespace kanso
+
+using namespace kanso;
+
+extern "C" {
+
+int32_t kanso_cuda_shard_range(int64_t n, int32_t rank, int32_t world, int64_t align,
+                               int64_t* begin, int64_t* count) {
+  if (!begin || !count || world < 1 || rank < 0 || rank >= world || align < 1 || n < 0 ||
+      n % align != 0)
+    return KANSO_ERR_SHAPE;
+  const int64_t units = n / align;
+  const int64_t b = units * rank / world, e = units * (rank + 1) / world;
+  *begin = b * align;
+  *count = (e - b) * align;
+  return KANSO_OK;
+}
+
+int32_t kanso_cuda_shard_k_repack(const void* host_bytes, int32_t dtype, int64_t rows,
+                                  int64_t cols, int64_t col_begin, int64_t col_count,
+                                  void* out_bytes, size_t out_capacity) {
+  int blk, bb;
+  if (dtype == KANSO_DTYPE_Q8_0) {
+    blk = 32;
+    bb = Q8_BYTES;
+  } else if (dtype == KANSO_DTYPE_Q4_K) {
+    blk = 256;
+    bb = Q4K_BYTES;
+  } else {
+    return KANSO_ERR_UNSUPPORTED;
+  }
+  if (!host_bytes || !out_bytes || rows < 0 || cols % blk || col_begin % blk || col_count % blk ||
+      col_begin < 0 || col_count < 0 || col_begin + col_count > cols)
+    return KANSO_ERR_SHAPE;
+  const size_t row_in = (size_t)(cols / blk) * bb, row_out = (size_t)(col_count / blk) * bb;
+  if (out_capacity < row_out * (size_t)rows) return KANSO_ERR_SHAPE;
+  const uint8_t* src = (const uint8_t*)host_bytes + (size_t)(col_begin / blk) * bb;
+  uint8_t* dst = (uint8_t*)out_bytes;
+  for (int64_t r = 0; r < rows; ++r) std::memcpy(dst + r * row_out, src + r * row_in, row_out);
+  return KANSO_OK;
+}
+
+int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
+                                      const float* x, int64_t M, float* const* y_out,
+                                      int32_t n_out, int64_t n_total, int64_t row_offset,
+                                      int32_t act_mode) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "linear_scatter_out: ctx is NULL");
+  if (!w || !x || !y_out) return fail(ctx, KANSO_ERR_SHAPE, "linear_scatter_out: NULL pointer");
+  if (n_out < 1 || n_out > 8)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED, "linear_scatter_out: %d result buffers (1..8)", n_out);
+  if (row_offset < 0 || row_offset + w->rows > n_total)
+    return fail(ctx, KANSO_ERR_SHAPE, "linear_scatter_out: rows [%lld, %lld) outside [0, %lld)",
+                (long long)row_offset, (long long)(row_offset + w->rows), (long long)n_total);
+  for (int o = 0; o < n_out; ++o)
+    if (!y_out[o]) return fail(ctx, KANSO_ERR_SHAPE, "linear_scatter_out: y_out[%d] is NULL", o);
+  if (M <= 0) return M == 0 ? KANSO_OK : fail(ctx, KANSO_ERR_SHAPE, "linear_scatter_out: M < 0");
+  if (w->dtype == KANSO_DTYPE_Q4_K && act_mode == KANSO_ACT_F32 && M <= 8) {
+    bool handled = false;
+    int32_t st = q4k_direct_matmul_out(ctx, w->dev, x, nullptr, M, w->rows, w->cols, &handled,
+                                       y_out, n_out, n_total, row_offset);
+    if (st || handled) return st;
+  }
+  // other shapes: compute the slice into scratch, then one small scatter kernel
+  float* tmp = nullptr;
+  {
+    // the matmul kernels may use the context scratch themselves: keep this slice in the
+    // device staging buffer
+    int32_t st = ctx_stage_dev(ctx, sizeof(float) * (size_t)M * w->rows);
+    if (st) return st;
+    tmp = (float*)ctx->stage_dev;
+  }
+  int32_t st = matmul_dispatch(ctx, w->dtype, w->dev, x, tmp, M, w->rows, w->cols, act_mode);
+  if (st) return st;
+  ScatterArgs sa;
+  sa.n_out = n_out;
+  for (int o = 0; o < 8; ++o) sa.out[o] = o < n_out ? y_out[o] : nullptr;
+  const int64_t n = M * w->rows;
+  scatter_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(tmp, sa, M, w->rows,
+                                                                           n_total, row_offset);
+  return after_launch(ctx, "linear_scatter_out");
+}
+
+}  // extern "C"
