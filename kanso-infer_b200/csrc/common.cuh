@@ -77,6 +77,14 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
       : "memory");
 }
 
+// Programmatic dependent launch: let the next kernel of the stream start launching, and wait
+// until the kernel before this one has completed and its writes are visible. Both are no-ops
+// for a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
 // unsigned bytes of a times signed bytes of b
 __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstdarg>
 #include <cstdio>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -47,6 +48,26 @@ int32_t ctx_pinned(kanso_cuda_ctx* ctx, size_t bytes);
 int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes);
 // Checks the launch, counts it.
 int32_t after_launch(kanso_cuda_ctx* ctx, const char* what);
+
+// Launches `kern` on the context's stream. When the context allows overlap
+// (KANSO_OPT_OVERLAP_WEIGHT_PREFETCH) the launch carries the programmatic-stream-serialization
+// attribute; such a kernel MUST execute griddepcontrol.wait before it touches anything an
+// earlier kernel may have written.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(kanso_cuda_ctx* ctx, void (*kern)(KArgs...), dim3 grid,
+                                    dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.dynamicSmemBytes = smem;
+  lc.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ctx->overlap_weight_prefetch ? 1 : 0;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  return cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

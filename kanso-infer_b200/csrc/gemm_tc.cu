@@ -23,9 +23,11 @@
 // Every mbarrier wait is bounded; on a timeout the CTA records DEV_WAIT_TIMEOUT, frees its
 // TMEM columns and returns.
 //
-// Numerics: both operands are rounded once to f16 (relative 2^-12 on average) and products
-// accumulate in f32; against the f32 reference this gives ~2-4e-4 of the output scale, inside
-// the 1e-3 bound. KANSO_ACT_Q8 (bit-exact int32 block sums) is not offered on this path: its
+// Numerics: a single f16 rounding of each operand (2^-12 on average) keeps one matmul inside
+// the 1e-3 bound but drifts past the 1e-2 logit bound over a stack of layers, so both
+// operands are split in two f16 terms, w = wh + wl and x = xh + xl (the remainders are exact
+// or near-exact), and each 16-wide K step issues three MMAs: wh*xh + wl*xh + wh*xl. Only the
+// wl*xl term (2^-22) is dropped; products accumulate in f32 in TMEM. KANSO_ACT_Q8 (bit-exact int32 block sums) is not offered on this path: its
 // per-32 scales would force the accumulator out of TMEM every K=32.
 #include "ctx.h"
 
@@ -34,7 +36,8 @@ namespace kanso {
 constexpr int TC_THREADS = 256;
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
-constexpr int TC_A_STAGE = TC_TILE_N * TC_KC * 2;  // bytes of f16 A per stage (16 KB)
+constexpr int TC_A_PLANE = TC_TILE_N * TC_KC * 2;  // bytes of one f16 A term per stage (16 KB)
+constexpr int TC_A_STAGE = 2 * TC_A_PLANE;         // hi and lo terms
 
 struct TcArgs {
   const uint8_t* w;
@@ -48,32 +51,34 @@ struct TcArgs {
   int* status;
 };
 
-// x f32 [M,K] -> f16, layout [stage][chunk of 8 k][row m][8 values]; rows >= M are zero.
-// perm: order of the values inside a chunk (Q4_K's nibble unpack yields k order 0,2,1,3,...).
+// x f32 [M,K] -> two f16 terms xh + xl, layout [stage][term][chunk of 8 k][row m][8 values];
+// rows >= M are zero.
 __global__ void tc_pack_activations_kernel(const float* __restrict__ x, __half* __restrict__ xp,
-                                           int M, int Mt, int K, int perm) {
+                                           int M, int Mt, int K) {
   const int64_t total = (int64_t)(K / 8) * Mt;  // one thread per (chunk, row)
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int m = (int)(i % Mt);
     const int chunk = (int)(i / Mt);  // global chunk index = k / 8
-    __align__(16) __half v[8];
+    __align__(16) __half hi[8], lo[8];
     if (m < M) {
       const float4* src = reinterpret_cast<const float4*>(x + (int64_t)m * K + chunk * 8);
-      const float4 a = __ldg(src), b = __ldg(src + 1);
+      const float4 a = src[0], b = src[1];
       const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        // perm: position p holds k = {0,2,1,3,4,6,5,7}[p]
-        const int k = perm ? ((j & 4) | ((j & 1) << 1) | ((j >> 1) & 1)) : j;
-        v[j] = __float2half_rn(f[k]);
+        hi[j] = __float2half_rn(f[j]);
+        lo[j] = __float2half_rn(f[j] - __half2float(hi[j]));
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(0.f);
+      for (int j = 0; j < 8; ++j) hi[j] = lo[j] = __float2half_rn(0.f);
     }
-    // [stage][chunk in stage][m][8]  ==  [chunk][m][8] since a stage is 8 consecutive chunks
-    *reinterpret_cast<uint4*>(xp + ((int64_t)chunk * Mt + m) * 8) = *reinterpret_cast<uint4*>(v);
+    const int stage = chunk >> 3, c = chunk & 7;
+    __half* base = xp + (int64_t)stage * (2 * 8 * Mt * 8);
+    *reinterpret_cast<uint4*>(base + ((int64_t)c * Mt + m) * 8) = *reinterpret_cast<uint4*>(hi);
+    *reinterpret_cast<uint4*>(base + ((int64_t)(8 + c) * Mt + m) * 8) =
+        *reinterpret_cast<uint4*>(lo);
   }
 }
 
@@ -171,21 +176,28 @@ __device__ __forceinline__ void tc_dequant_q8_0(const TcArgs& a, int64_t n, int 
   const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128, exact in f16
 #pragma unroll
   for (int c = 0; c < 4; ++c) {  // chunk of 8 weights = two words of int8
-    uint32_t out[4];
+    uint32_t out[4], rem[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint32_t q = __funnelshift_r(v[2 * c + h], v[2 * c + h + 1], 16) ^ 0x80808080u;
       // 0x6400 | byte = 1024 + (q + 128) as f16, exactly
       uint32_t p01 = __byte_perm(q, 0x64646464u, 0x4140);
       uint32_t p23 = __byte_perm(q, 0x64646464u, 0x4342);
-      __half2 h01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), bias), d2);
-      __half2 h23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), bias), d2);
+      const __half2 q01 = __hsub2(*reinterpret_cast<__half2*>(&p01), bias);
+      const __half2 q23 = __hsub2(*reinterpret_cast<__half2*>(&p23), bias);
+      __half2 h01 = __hmul2(q01, d2), h23 = __hmul2(q23, d2);
+      // d*q - round(d*q): the fused multiply-add forms the product exactly
+      __half2 l01 = __hfma2(q01, d2, __hneg2(h01)), l23 = __hfma2(q23, d2, __hneg2(h23));
       out[2 * h] = *reinterpret_cast<uint32_t*>(&h01);
       out[2 * h + 1] = *reinterpret_cast<uint32_t*>(&h23);
+      rem[2 * h] = *reinterpret_cast<uint32_t*>(&l01);
+      rem[2 * h + 1] = *reinterpret_cast<uint32_t*>(&l23);
     }
     const int kc = blk * 4 + c;  // chunk of 8 k-values within the stage
     *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
         make_uint4(out[0], out[1], out[2], out[3]);
+    *reinterpret_cast<uint4*>(As + TC_A_PLANE + kc * (TC_TILE_N * 16) + row * 16) =
+        make_uint4(rem[0], rem[1], rem[2], rem[3]);
   }
 }
 
@@ -211,7 +223,7 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcArgs& a, int64_t n, int 
   const int sh0 = 4 * half;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t out[4];
+    uint32_t out[4], rem[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint32_t w = qw[2 * c + h] >> sh0;
@@ -223,12 +235,19 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcArgs& a, int64_t n, int 
       }
       __half2 h01 = __floats2half2_rn(f[0], f[1]);
       __half2 h23 = __floats2half2_rn(f[2], f[3]);
+      const float2 g01 = __half22float2(h01), g23 = __half22float2(h23);
+      __half2 l01 = __floats2half2_rn(f[0] - g01.x, f[1] - g01.y);
+      __half2 l23 = __floats2half2_rn(f[2] - g23.x, f[3] - g23.y);
       out[2 * h] = *reinterpret_cast<uint32_t*>(&h01);
       out[2 * h + 1] = *reinterpret_cast<uint32_t*>(&h23);
+      rem[2 * h] = *reinterpret_cast<uint32_t*>(&l01);
+      rem[2 * h + 1] = *reinterpret_cast<uint32_t*>(&l23);
     }
     const int kc = half * 4 + c;  // low nibbles: k 0..31 of the group, high nibbles: 32..63
     *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
         make_uint4(out[0], out[1], out[2], out[3]);
+    *reinterpret_cast<uint4*>(As + TC_A_PLANE + kc * (TC_TILE_N * 16) + row * 16) =
+        make_uint4(rem[0], rem[1], rem[2], rem[3]);
   }
 }
 
@@ -236,7 +255,8 @@ template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t b_stage = 8u * a.Mt * 16u;  // bytes of the B tile of one stage
+  const uint32_t b_plane = 8u * a.Mt * 16u;  // bytes of one term of the B tile of a stage
+  const uint32_t b_stage = 2u * b_plane;
   uint8_t* As = smem;
   uint8_t* Bs = smem + 2 * TC_A_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(Bs + 2 * b_stage);
@@ -287,9 +307,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
       const uint32_t a_addr = smem_u32(Ab), b_addr = smem_u32(Bb);
 #pragma unroll
       for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
-        const uint64_t ad = tc_smem_desc(a_addr + j * 2 * (TC_TILE_N * 16), TC_TILE_N * 16, 128);
-        const uint64_t bd = tc_smem_desc(b_addr + j * 2 * (a.Mt * 16), a.Mt * 16, 128);
-        tc_mma_f16(tmem_base, ad, bd, idesc, (it > 0 || j > 0) ? 1u : 0u);
+        const uint32_t ao = j * 2 * (TC_TILE_N * 16), bo = j * 2 * (a.Mt * 16);
+        const uint64_t ah = tc_smem_desc(a_addr + ao, TC_TILE_N * 16, 128);
+        const uint64_t al = tc_smem_desc(a_addr + TC_A_PLANE + ao, TC_TILE_N * 16, 128);
+        const uint64_t bh = tc_smem_desc(b_addr + bo, a.Mt * 16, 128);
+        const uint64_t bl = tc_smem_desc(b_addr + b_plane + bo, a.Mt * 16, 128);
+        tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
+        tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
+        tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
       }
       tc_commit(&bars[buf]);
     }
@@ -343,14 +368,14 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   // split K until the grid covers the SMs about twice, keeping >= 4 stages per CTA
   int ksplit = 1;
   while (tiles_n * ksplit < 2 * ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
-  const size_t xp_bytes = (size_t)(K / 8) * Mt * 16;
+  const size_t xp_bytes = 2 * (size_t)(K / 8) * Mt * 16;
   uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
   if (!scratch) return KANSO_ERR_DEVICE;
   *handled = true;
 
   const int64_t chunks = (K / 8) * Mt;
   tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
-      x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, 0);
+      x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
   int32_t st = after_launch(ctx, "gemm_tc pack activations");
   if (st) return st;
   if (ksplit > 1)
@@ -369,7 +394,7 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   a.ksplit = ksplit;
   a.stages_total = stages_total;
   a.status = ctx->dev_status;
-  const size_t smem = 2 * TC_A_STAGE + 2 * (size_t)(8 * Mt * 16) + 64;
+  const size_t smem = 2 * TC_A_STAGE + 2 * (size_t)(2 * 8 * Mt * 16) + 64;
   auto kern = dtype == KANSO_DTYPE_Q8_0 ? gemm_tc_kernel<TC_FMT_Q8_0> : gemm_tc_kernel<TC_FMT_Q4_K>;
   static bool attr_set[2][16] = {};
   bool& done = attr_set[dtype == KANSO_DTYPE_Q8_0 ? 0 : 1][ctx->device & 15];

@@ -43,13 +43,29 @@ struct Fmt<FMT_Q4_K> {
 constexpr int MAX_STAGES = 4;
 constexpr int MAX_WARPS = 16;
 
-struct StreamArgs {
+constexpr int MAX_SEGS = 3;
+// One weight matrix of a launch. A launch may carry up to three matrices that share the
+// activations (Q, K, V or gate, up): CTAs [cta_begin, next cta_begin) work on segment i.
+struct StreamSeg {
   const uint8_t* w;
-  const float* x;
   float* y;
   int64_t rows;         // weight rows (N)
   int64_t total_bytes;  // rows * row_bytes
-  int64_t ldx, ldy;     // elements between activation rows in x / y
+  int64_t ldy;          // elements between activation rows in y
+  int cta_begin;
+};
+
+struct StreamArgs {
+  StreamSeg seg[MAX_SEGS];
+  int nseg;
+  const float* x;
+  // optional fusions of the decode step (src/model.rs:1141-1207):
+  const float* x2;      // activations are silu(x) * x2 (the SwiGLU product feeding ffn_down)
+  const float* norm_w;  // activations are rmsnorm(x) * norm_w (attn_norm / ffn_norm / final norm)
+  float eps;
+  const float* resid;   // result is resid + W.x (residual add); may alias y
+  int64_t ldr;
+  int64_t ldx;          // elements between activation rows in x
   int K, bpr, row_bytes;
   int M;                // activation rows handled by this launch
   int tile_rows;        // rows per bulk copy (multiple of rows-per-warp-iteration)
@@ -99,13 +115,56 @@ __device__ __forceinline__ void stage_activations(const StreamArgs& a, const Str
   const int total = a.M * per_row;
   float* xscale = reinterpret_cast<float*>(smem + L.off_scale);
   float* xsum = reinterpret_cast<float*>(smem + L.off_sum);
+  // rmsnorm fold (src/model.rs:653-659): 1 / sqrt(mean(x^2) + eps) per activation row
+  __shared__ float s_inv_rms[8];
+  __shared__ float s_red[32];
+  if (a.norm_w) {
+    for (int m = 0; m < a.M; ++m) {
+      const float4* xr = reinterpret_cast<const float4*>(a.x + (int64_t)m * a.ldx);
+      float ss = 0.f;
+      for (int c = threadIdx.x; c < per_row; c += blockDim.x) {
+        const float4 t = xr[c];
+        ss += (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? s_red[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        if (threadIdx.x == 0) s_inv_rms[m] = 1.0f / sqrtf(t / (float)a.K + a.eps);
+      }
+    }
+    __syncthreads();
+  }
   for (int base = 0; base < total; base += blockDim.x) {
     int i = base + threadIdx.x;
     bool on = i < total;
     int m = on ? i / per_row : 0;
     int c4 = on ? i - m * per_row : 0;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (on) v = __ldg(reinterpret_cast<const float4*>(a.x + (int64_t)m * a.ldx) + c4);
+    if (on) {
+      // plain loads: with dependent launch the producer kernel has just finished
+      v = reinterpret_cast<const float4*>(a.x + (int64_t)m * a.ldx)[c4];
+      if (a.x2) {  // silu(g) * u with silu(g) = g / (1 + e^-g), src/model.rs:367-382
+        const float4 u = reinterpret_cast<const float4*>(a.x2 + (int64_t)m * a.ldx)[c4];
+        v.x = v.x / (1.0f + expf(-v.x)) * u.x;
+        v.y = v.y / (1.0f + expf(-v.y)) * u.y;
+        v.z = v.z / (1.0f + expf(-v.z)) * u.z;
+        v.w = v.w / (1.0f + expf(-v.w)) * u.w;
+      }
+      if (a.norm_w) {
+        const float4 nw = __ldg(reinterpret_cast<const float4*>(a.norm_w) + c4);
+        const float r = s_inv_rms[m];
+        v.x = v.x * r * nw.x;
+        v.y = v.y * r * nw.y;
+        v.z = v.z * r * nw.z;
+        v.w = v.w * r * nw.w;
+      }
+    }
     float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
@@ -284,13 +343,18 @@ __global__ void __launch_bounds__(MAX_WARPS * 32)
   uint8_t* my_stages = smem + L.off_stages + warp * a.nstage * a.stage_bytes;
   const int nblk = a.K / 32;
 
-  // rows of this CTA, and the tiles of this warp within them
-  const int64_t rb = a.rows * blockIdx.x / gridDim.x;
-  const int64_t re = a.rows * (blockIdx.x + 1) / gridDim.x;
+  // the matrix this CTA works on, then its rows there and the tiles of this warp within them
+  int sg = 0;
+  while (sg + 1 < a.nseg && (int)blockIdx.x >= a.seg[sg + 1].cta_begin) ++sg;
+  const StreamSeg& S = a.seg[sg];
+  const int cta = (int)blockIdx.x - S.cta_begin;
+  const int nctas = (sg + 1 < a.nseg ? a.seg[sg + 1].cta_begin : (int)gridDim.x) - S.cta_begin;
+  const int64_t rb = S.rows * cta / nctas;
+  const int64_t re = S.rows * (cta + 1) / nctas;
   const int TR = a.tile_rows;
   const int ntiles_cta = (int)((re - rb + TR - 1) / TR);
   const int n_my = warp < ntiles_cta ? (ntiles_cta - warp + nwarps - 1) / nwarps : 0;
-  const int64_t total16 = a.total_bytes & ~int64_t(15);
+  const int64_t total16 = S.total_bytes & ~int64_t(15);
 
   if (lane == 0)
     for (int s = 0; s < a.nstage; ++s) mbar_init(&bars[s], 1);
@@ -309,16 +373,21 @@ __global__ void __launch_bounds__(MAX_WARPS * 32)
     if (a1 > total16) {
       // the stream ends inside a 16-byte unit: fetch that ragged end with plain loads
       a1 = total16;
-      for (int64_t t = a1; t < b1; ++t) dst[t - a0] = a.w[t];
+      for (int64_t t = a1; t < b1; ++t) dst[t - a0] = S.w[t];
     }
     const uint32_t bytes = (uint32_t)(a1 - a0);
     mbar_arrive_expect_tx(&bars[s], bytes);
-    bulk_g2s(dst, a.w + a0, bytes, &bars[s]);
+    bulk_g2s(dst, S.w + a0, bytes, &bars[s]);
   };
   int issued = 0;
   if (lane == 0)
     for (; issued < n_my && issued < a.nstage; ++issued) issue(issued);
   issued = __shfl_sync(0xFFFFFFFFu, issued, 0);
+
+  // Programmatic dependent launch: the weight copies above never depend on the kernel before
+  // this one; the activations (and the residual) may, so everything below waits for it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   stage_activations<FMT, PLANES>(a, L, smem);
   __syncthreads();
@@ -368,7 +437,10 @@ __global__ void __launch_bounds__(MAX_WARPS * 32)
           float u = __shfl_down_sync(0xFFFFFFFFu, v, o);
           if (lcol + o < seg) v += u;
         }
-        if (lane_on && lcol == 0 && row < nr) a.y[(int64_t)m * a.ldy + r0 + row] = v;
+        if (lane_on && lcol == 0 && row < nr) {
+          if (a.resid) v += a.resid[(int64_t)m * a.ldr + r0 + row];
+          S.y[(int64_t)m * S.ldy + r0 + row] = v;
+        }
       }
     }
     __syncwarp();
@@ -385,31 +457,74 @@ __global__ void __launch_bounds__(MAX_WARPS * 32)
   }
 }
 
+// What one launch computes: up to three matrices over shared activations, with the optional
+// fusions of the decode step.
+struct StreamCall {
+  int nseg = 1;
+  const void* w[MAX_SEGS] = {nullptr, nullptr, nullptr};
+  float* y[MAX_SEGS] = {nullptr, nullptr, nullptr};
+  int64_t rows[MAX_SEGS] = {0, 0, 0};
+  const float* x = nullptr;
+  const float* x2 = nullptr;
+  const float* norm_w = nullptr;
+  float eps = 0.f;
+  const float* resid = nullptr;
+  int64_t K = 0;
+  int M = 1;
+};
+
 template <int FMT, int MT, int PLANES>
-static int32_t launch_stream(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
-                             int64_t rows, int64_t K, int M, int64_t ldx, int64_t ldy) {
+static int32_t launch_stream(kanso_cuda_ctx* ctx, const StreamCall& c) {
   using F = Fmt<FMT>;
   StreamArgs a;
-  a.w = (const uint8_t*)w;
-  a.x = x;
-  a.y = y;
-  a.rows = rows;
-  a.K = (int)K;
-  a.bpr = (int)(K / F::ITEM_ELEMS);
+  a.K = (int)c.K;
+  a.bpr = (int)(c.K / F::ITEM_ELEMS);
   a.row_bytes = a.bpr * F::ITEM_BYTES;
-  a.total_bytes = rows * a.row_bytes;
-  a.ldx = ldx;
-  a.ldy = ldy;
-  a.M = M;
+  a.nseg = c.nseg;
+  a.x = c.x;
+  a.x2 = c.x2;
+  a.norm_w = c.norm_w;
+  a.eps = c.eps;
+  a.resid = c.resid;
+  a.ldx = c.K;
+  a.M = c.M;
   a.status = ctx->dev_status;
+  int64_t total_rows = 0, max_rows = 0;
+  for (int i = 0; i < c.nseg; ++i) {
+    total_rows += c.rows[i];
+    if (c.rows[i] > max_rows) max_rows = c.rows[i];
+  }
+  // CTAs are dealt to the matrices in proportion to their rows
+  int grid = ctx->sm_count;
+  if (total_rows < grid) grid = (int)total_rows;
+  if (grid < c.nseg) grid = c.nseg;
+  int cta = 0;
+  int64_t rows_per_cta = 1;
+  for (int i = 0; i < MAX_SEGS; ++i) {
+    StreamSeg& sgm = a.seg[i];
+    if (i < c.nseg) {
+      sgm.w = (const uint8_t*)c.w[i];
+      sgm.y = c.y[i];
+      sgm.rows = c.rows[i];
+      sgm.total_bytes = c.rows[i] * a.row_bytes;
+      sgm.ldy = c.rows[i];
+      sgm.cta_begin = cta;
+      int n = i + 1 == c.nseg ? grid - cta
+                              : (int)((c.rows[i] * grid + total_rows / 2) / total_rows);
+      if (n < 1) n = 1;
+      if (n > grid - cta - (c.nseg - 1 - i)) n = grid - cta - (c.nseg - 1 - i);
+      const int64_t rpc = (c.rows[i] + n - 1) / n;
+      if (rpc > rows_per_cta) rows_per_cta = rpc;
+      cta += n;
+    } else {
+      sgm = StreamSeg{nullptr, nullptr, 0, 0, 0, grid};
+    }
+  }
+  a.ldr = c.rows[0];  // the residual has the shape of the (single) result
 
   const int R = a.bpr <= 32 ? 32 / a.bpr : 1;
-  int grid = ctx->sm_count;
-  if (rows < grid) grid = (int)rows;
-  const int64_t rows_per_cta = (rows + grid - 1) / grid;
-
   // Pick warps, tile rows and stages so the rings fit in shared memory.
-  const int smem_max = ctx->smem_optin;
+  const int smem_max = ctx->smem_optin - 1024;  // the kernel also has a little static shared memory
   int best_w = 0, best_s = 0, best_tr = 0, best_sb = 0;
   for (int nw : {8, 4, 2, 1}) {
     // tile: about 4 KB, whole passes of R rows, no more than this warp's share of the CTA's rows
@@ -420,11 +535,11 @@ static int32_t launch_stream(kanso_cuda_ctx* ctx, const void* w, const float* x,
     if (tr > share) tr = (int)share;
     if (tr < R) tr = R;
     int sb = ((tr * a.row_bytes + 15) & ~15) + 32;
-    for (int s = MAX_STAGES; s >= 2; --s) {
-      StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, M, nw, s, sb);
+    for (int st = MAX_STAGES; st >= 2; --st) {
+      StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, c.M, nw, st, sb);
       if (L.total <= smem_max) {
         best_w = nw;
-        best_s = s;
+        best_s = st;
         best_tr = tr;
         best_sb = sb;
         break;
@@ -436,38 +551,90 @@ static int32_t launch_stream(kanso_cuda_ctx* ctx, const void* w, const float* x,
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "gemv: K=%lld with %d activation rows does not fit the %d-byte shared memory of "
                 "one SM",
-                (long long)K, M, smem_max);
+                (long long)c.K, c.M, smem_max);
   a.tile_rows = best_tr;
   a.stage_bytes = best_sb;
   a.nstage = best_s;
-  StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, M, best_w, best_s, best_sb);
+  StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, c.M, best_w, best_s, best_sb);
   auto kern = gemv_stream_kernel<FMT, MT, PLANES>;
   static int smem_set[16] = {0};  // per device: largest opt-in already made for this kernel
   if (L.total > smem_set[ctx->device & 15]) {
     KANSO_CUDA_TRY(ctx,
                    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        ctx->smem_optin),
+                                        smem_max),
                    "gemv: shared memory opt-in");
-    smem_set[ctx->device & 15] = ctx->smem_optin;
+    smem_set[ctx->device & 15] = smem_max;
   }
-  kern<<<grid, best_w * 32, L.total, ctx->stream>>>(a);
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(best_w * 32);
+  lc.dynamicSmemBytes = L.total;
+  lc.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ctx->overlap_weight_prefetch ? 1 : 0;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  KANSO_CUDA_TRY(ctx, cudaLaunchKernelEx(&lc, kern, a), "gemv_stream launch");
   return after_launch(ctx, "gemv_stream");
+}
+
+template <int FMT, int PLANES>
+static int32_t dispatch_call(kanso_cuda_ctx* ctx, const StreamCall& c) {
+  switch (c.M) {
+    case 1: return launch_stream<FMT, 1, PLANES>(ctx, c);
+    case 2: return launch_stream<FMT, 2, PLANES>(ctx, c);
+    case 3:
+    case 4: return launch_stream<FMT, 4, PLANES>(ctx, c);
+    default: return launch_stream<FMT, 8, PLANES>(ctx, c);
+  }
 }
 
 template <int FMT, int PLANES>
 static int32_t dispatch_m(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
                           int64_t rows, int64_t K, int M, int64_t ldx, int64_t ldy) {
-  switch (M) {
-    case 1:
-      return launch_stream<FMT, 1, PLANES>(ctx, w, x, y, rows, K, M, ldx, ldy);
-    case 2:
-      return launch_stream<FMT, 2, PLANES>(ctx, w, x, y, rows, K, M, ldx, ldy);
-    case 3:
-    case 4:
-      return launch_stream<FMT, 4, PLANES>(ctx, w, x, y, rows, K, M, ldx, ldy);
-    default:
-      return launch_stream<FMT, 8, PLANES>(ctx, w, x, y, rows, K, M, ldx, ldy);
+  (void)ldx;
+  (void)ldy;
+  StreamCall c;
+  c.w[0] = w;
+  c.y[0] = y;
+  c.rows[0] = rows;
+  c.x = x;
+  c.K = K;
+  c.M = M;
+  return dispatch_call<FMT, PLANES>(ctx, c);
+}
+
+// Fused decode-step matmul on Q8_0 weights, at most 8 activation rows: up to three matrices
+// over the same activations, rmsnorm folded into the activation staging, silu(x)*x2 as the
+// activations, residual added to the result. Declared in glue.cuh.
+int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
+                          const int64_t* rows, const float* x, const float* x2,
+                          const float* norm_w, float eps, const float* resid, int64_t K, int M,
+                          int32_t act_mode) {
+  if (nseg < 1 || nseg > MAX_SEGS || M < 1 || M > 8 || K <= 0 || K % 32 != 0)
+    return fail(ctx, KANSO_ERR_SHAPE, "fused matmul: bad shape (nseg %d, M %d, K %lld)", nseg, M,
+                (long long)K);
+  if (resid && nseg != 1)
+    return fail(ctx, KANSO_ERR_SHAPE, "fused matmul: a residual needs a single matrix");
+  StreamCall c;
+  c.nseg = nseg;
+  for (int i = 0; i < nseg; ++i) {
+    if (!w[i] || !y[i] || rows[i] < 1 || !aligned16(w[i]))
+      return fail(ctx, KANSO_ERR_SHAPE, "fused matmul: matrix %d is missing or misaligned", i);
+    c.w[i] = w[i];
+    c.y[i] = y[i];
+    c.rows[i] = rows[i];
   }
+  c.x = x;
+  c.x2 = x2;
+  c.norm_w = norm_w;
+  c.eps = eps;
+  c.resid = resid;
+  c.K = K;
+  c.M = M;
+  return act_mode == KANSO_ACT_Q8 ? dispatch_call<FMT_Q8_0, 1>(ctx, c)
+                                  : dispatch_call<FMT_Q8_0, 2>(ctx, c);
 }
 
 // y[M,N] = x[M,K] @ W[N,K]^T with the streaming kernel, at most 8 activation rows per pass.

@@ -36,9 +36,18 @@ int32_t launch_rmsnorm(kanso_cuda_ctx* ctx, const float* x, const float* w, floa
 int32_t launch_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, int64_t T,
                     int64_t heads, int64_t head_dim, float theta, const float* cos_t,
                     const float* sin_t, int table_len);
+struct KvGeom;
+int32_t launch_rope_kv_write(kanso_cuda_ctx* ctx, float* q, const float* k, const float* v,
+                             const uint32_t* positions, const uint32_t* slots, int64_t T, int H,
+                             const float* cos_t, const float* sin_t, int table_len,
+                             const KvGeom& g, uint32_t layer);
 int32_t launch_silu_mul(kanso_cuda_ctx* ctx, const float* g, const float* u, float* out,
                         int64_t n);
 int32_t launch_residual_add(kanso_cuda_ctx* ctx, float* h, const float* p, int64_t n);
+int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
+                          const int64_t* rows, const float* x, const float* x2,
+                          const float* norm_w, float eps, const float* resid, int64_t K, int M,
+                          int32_t act_mode);
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode);
 

@@ -279,6 +279,67 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
                                                  m->hidden, m->token_embd.rows, (int)hidden,
                                                  ctx->dev_status);
   if ((st = after_launch(ctx, "embed"))) return st;
+  const ModelLin& head = m->output.dev ? m->output : m->token_embd;  // tied lm_head
+
+  // Up to 8 sequences on Q8_0 weights: 7 launches per layer. The norms are folded into the
+  // activation staging of the projections that follow them, SiLU*up into ffn_down's, the
+  // residual adds into the epilogues, RoPE and the KV write into one kernel.
+  bool fused = B <= 8 && head.dtype == KANSO_DTYPE_Q8_0;
+  for (uint32_t l = 0; l < c.num_hidden_layers && fused; ++l)
+    for (const auto& w : m->layers[l].w) fused = fused && w.dev && w.dtype == KANSO_DTYPE_Q8_0;
+  if (fused) {
+    const KvGeom g = kv_geom(kv);
+    for (uint32_t l = 0; l < c.num_hidden_layers; ++l) {
+      auto& ly = m->layers[l];
+      if (!ly.attn_norm || !ly.ffn_norm)
+        return fail(ctx, KANSO_ERR_CONFIG, "decode_step: norm weights of layer %u not set", l);
+      {
+        const void* w3[3] = {ly.w[KANSO_W_ATTN_Q].dev, ly.w[KANSO_W_ATTN_K].dev,
+                             ly.w[KANSO_W_ATTN_V].dev};
+        float* y3[3] = {q, k, v};
+        const int64_t r3[3] = {(int64_t)qw, (int64_t)kw, (int64_t)kw};
+        if ((st = stream_fused_q8_0(ctx, 3, w3, y3, r3, m->hidden, nullptr, ly.attn_norm,
+                                    c.rms_norm_eps, nullptr, hidden, (int)B, act_mode)))
+          return st;
+      }
+      if ((st = launch_rope_kv_write(ctx, q, k, v, positions, slots, B, (int)H, m->rope_cos,
+                                     m->rope_sin, m->rope_len, g, l)))
+        return st;
+      if ((st = launch_paged_attention(ctx, kv, l, q, block_tables, context_lens, m->attn, &pa,
+                                       max_ctx)))
+        return st;
+      {
+        const void* w1[1] = {ly.w[KANSO_W_ATTN_OUTPUT].dev};
+        float* y1[1] = {m->hidden};
+        const int64_t r1[1] = {(int64_t)hidden};
+        if ((st = stream_fused_q8_0(ctx, 1, w1, y1, r1, m->attn, nullptr, nullptr, 0.f, m->hidden,
+                                    qw, (int)B, act_mode)))
+          return st;
+      }
+      {
+        const void* w2[2] = {ly.w[KANSO_W_FFN_GATE].dev, ly.w[KANSO_W_FFN_UP].dev};
+        float* y2[2] = {m->gate, m->up};
+        const int64_t r2[2] = {(int64_t)inter, (int64_t)inter};
+        if ((st = stream_fused_q8_0(ctx, 2, w2, y2, r2, m->hidden, nullptr, ly.ffn_norm,
+                                    c.rms_norm_eps, nullptr, hidden, (int)B, act_mode)))
+          return st;
+      }
+      {
+        const void* w1[1] = {ly.w[KANSO_W_FFN_DOWN].dev};
+        float* y1[1] = {m->hidden};
+        const int64_t r1[1] = {(int64_t)hidden};
+        if ((st = stream_fused_q8_0(ctx, 1, w1, y1, r1, m->gate, m->up, nullptr, 0.f, m->hidden,
+                                    inter, (int)B, act_mode)))
+          return st;
+      }
+    }
+    const void* w1[1] = {head.dev};
+    float* y1[1] = {logits_dev};
+    const int64_t r1[1] = {head.rows};
+    return stream_fused_q8_0(ctx, 1, w1, y1, r1, m->hidden, nullptr, m->final_norm,
+                             c.rms_norm_eps, nullptr, hidden, (int)B, act_mode);
+  }
+
   for (uint32_t l = 0; l < c.num_hidden_layers; ++l) {
     auto& ly = m->layers[l];
     if (!ly.attn_norm || !ly.ffn_norm)
@@ -288,13 +349,9 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_Q], m->normed, q, B, act_mode))) return st;
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_K], m->normed, k, B, act_mode))) return st;
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_V], m->normed, v, B, act_mode))) return st;
-    if ((st = launch_rope(ctx, q, positions, B, H, hd, c.rope_theta, m->rope_cos, m->rope_sin,
-                          m->rope_len)))
+    if ((st = launch_rope_kv_write(ctx, q, k, v, positions, slots, B, (int)H, m->rope_cos,
+                                   m->rope_sin, m->rope_len, kv_geom(kv), l)))
       return st;
-    if ((st = launch_rope(ctx, k, positions, B, KH, hd, c.rope_theta, m->rope_cos, m->rope_sin,
-                          m->rope_len)))
-      return st;
-    if ((st = launch_kv_write(ctx, kv, l, slots, k, v, B, kw, kw))) return st;
     if ((st = launch_paged_attention(ctx, kv, l, q, block_tables, context_lens, m->attn, &pa,
                                      max_ctx)))
       return st;
@@ -310,7 +367,6 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
   }
   if ((st = launch_rmsnorm(ctx, m->hidden, m->final_norm, m->normed, B, hidden, c.rms_norm_eps)))
     return st;
-  const ModelLin& head = m->output.dev ? m->output : m->token_embd;  // tied lm_head
   return lin(ctx, head, m->normed, logits_dev, B, act_mode);
 }
 

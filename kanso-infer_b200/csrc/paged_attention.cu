@@ -47,6 +47,8 @@ __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
 template <int G>
 __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();  // q, the table and the pool rows of the new token come from earlier kernels
   const uint32_t hd = a.g.head_dim, bs = a.g.block_size;
   const uint32_t part = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const uint32_t ctx = a.lens[seq];
@@ -212,6 +214,8 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
 // Stage 2: merge the partitions of one (sequence, head)
 // (paged_attention_v2_reduce_kernel's role, src/metal/kernels/paged_attention_v2.metal:154-205).
 __global__ void paged_attn_stage2(const PaArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t head = blockIdx.x, seq = blockIdx.y, hd = a.g.head_dim;
   const uint32_t ctx = a.lens[seq];
   const size_t hidx = (size_t)seq * a.num_heads + head;
@@ -265,7 +269,7 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
 }
 
 template <int G>
-static void launch_stage1(const PaArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
   static size_t smem_set[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -274,7 +278,7 @@ static void launch_stage1(const PaArgs& a, dim3 grid, size_t smem, cudaStream_t 
                          (int)smem);
     smem_set[dev & 15] = smem;
   }
-  paged_attn_stage1<G><<<grid, PA_THREADS, smem, s>>>(a);
+  launch_dependent(ctx, paged_attn_stage1<G>, grid, dim3(PA_THREADS), smem, a);
 }
 
 int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
@@ -328,18 +332,18 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
                 smem);
   dim3 grid(nparts, p->num_kv_heads, p->num_seqs);
   switch (G) {
-    case 1: launch_stage1<1>(a, grid, smem, ctx->stream); break;
-    case 2: launch_stage1<2>(a, grid, smem, ctx->stream); break;
-    case 3: launch_stage1<3>(a, grid, smem, ctx->stream); break;
-    case 4: launch_stage1<4>(a, grid, smem, ctx->stream); break;
-    case 5: launch_stage1<5>(a, grid, smem, ctx->stream); break;
-    case 6: launch_stage1<6>(a, grid, smem, ctx->stream); break;
-    case 7: launch_stage1<7>(a, grid, smem, ctx->stream); break;
-    default: launch_stage1<8>(a, grid, smem, ctx->stream); break;
+    case 1: launch_stage1<1>(ctx, a, grid, smem); break;
+    case 2: launch_stage1<2>(ctx, a, grid, smem); break;
+    case 3: launch_stage1<3>(ctx, a, grid, smem); break;
+    case 4: launch_stage1<4>(ctx, a, grid, smem); break;
+    case 5: launch_stage1<5>(ctx, a, grid, smem); break;
+    case 6: launch_stage1<6>(ctx, a, grid, smem); break;
+    case 7: launch_stage1<7>(ctx, a, grid, smem); break;
+    default: launch_stage1<8>(ctx, a, grid, smem); break;
   }
   int32_t st = after_launch(ctx, "paged_attention stage 1");
   if (st) return st;
-  paged_attn_stage2<<<dim3(p->num_heads, p->num_seqs), 64, 0, ctx->stream>>>(a);
+  launch_dependent(ctx, paged_attn_stage2, dim3(p->num_heads, p->num_seqs), dim3(64), 0, a);
   return after_launch(ctx, "paged_attention stage 2");
 }
 
@@ -501,18 +505,18 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
                 "paged_attention_noalloc: %zu bytes of shared memory needed", smem);
   dim3 grid(nparts, p->num_kv_heads, p->num_seqs);
   switch (G) {
-    case 1: launch_stage1<1>(a, grid, smem, ctx->stream); break;
-    case 2: launch_stage1<2>(a, grid, smem, ctx->stream); break;
-    case 3: launch_stage1<3>(a, grid, smem, ctx->stream); break;
-    case 4: launch_stage1<4>(a, grid, smem, ctx->stream); break;
-    case 5: launch_stage1<5>(a, grid, smem, ctx->stream); break;
-    case 6: launch_stage1<6>(a, grid, smem, ctx->stream); break;
-    case 7: launch_stage1<7>(a, grid, smem, ctx->stream); break;
-    default: launch_stage1<8>(a, grid, smem, ctx->stream); break;
+    case 1: launch_stage1<1>(ctx, a, grid, smem); break;
+    case 2: launch_stage1<2>(ctx, a, grid, smem); break;
+    case 3: launch_stage1<3>(ctx, a, grid, smem); break;
+    case 4: launch_stage1<4>(ctx, a, grid, smem); break;
+    case 5: launch_stage1<5>(ctx, a, grid, smem); break;
+    case 6: launch_stage1<6>(ctx, a, grid, smem); break;
+    case 7: launch_stage1<7>(ctx, a, grid, smem); break;
+    default: launch_stage1<8>(ctx, a, grid, smem); break;
   }
   st = after_launch(ctx, "paged_attention_noalloc stage 1");
   if (st) return st;
-  paged_attn_stage2<<<dim3(p->num_heads, p->num_seqs), 64, 0, ctx->stream>>>(a);
+  launch_dependent(ctx, paged_attn_stage2, dim3(p->num_heads, p->num_seqs), dim3(64), 0, a);
   return after_launch(ctx, "paged_attention_noalloc stage 2");
 }
 

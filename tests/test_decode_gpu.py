@@ -138,3 +138,87 @@ def test_decode_batch_of_ragged_sequences(ctx, kb, oracle, torch_cuda):
     with pytest.raises(kb.KansoError) as e:
         gm.decode_step(gpool, tokens, positions, bad, padded, np.array(lens, np.uint32), maxb, got)
     assert e.value.code == kb.ERR_SHAPE
+
+
+@pytest.mark.parametrize("B,overlap", [(3, 1), (3, 0), (12, 1)])
+def test_decode_smollm2_shapes(kb, oracle, torch_cuda, B, overlap):
+    """SmolLM2-360M layer geometry (hidden 960, 15 query / 5 KV heads, head_dim 64, SwiGLU 2560,
+    vocab 49152, RoPE theta 100000, 16-token blocks, permuted block tables), two layers, ragged
+    contexts; B <= 8 takes the fused kernels, B = 12 the tensor-core GEMM. Logits within 1e-2 and
+    the same greedy token as the oracle engine."""
+    torch = torch_cuda
+    ctx = kb.Context(0, torch.cuda.current_stream())
+    ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, overlap)
+    L, hidden, H, KH, inter, vocab, bs = 2, 960, 15, 5, 2560, 49152, 16
+    hd = hidden // H
+    rng = np.random.Generator(np.random.PCG64(0xB2000D00 + B))
+    ocfg = oracle.ModelConfig(hidden, H, KH, L, inter, vocab, bs, 1024, 1e-5, 100000.0)
+    gcfg = kb.ModelConfig(hidden, H, KH, L, inter, vocab, bs, 1024, 1e-5, 100000.0)
+    om, gm = oracle.Model(ocfg), kb.Model(ctx, gcfg)
+    shapes = {0: (H * hd, hidden), 1: (KH * hd, hidden), 2: (KH * hd, hidden),
+              3: (hidden, H * hd), 4: (inter, hidden), 5: (inter, hidden), 6: (hidden, inter)}
+    for l in range(L):
+        for which, (r, c) in shapes.items():
+            blocks = oracle.quantize_weights_q8_0((rng.standard_normal((r, c)) * 0.02)
+                                                 .astype(np.float32))
+            assert om.set_weight(l, which, blocks, r, c) == 0
+            gm.set_weight(l, which, blocks, kb.DTYPE_Q8_0, r, c)
+        for which in (0, 1):
+            nw = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+            om.set_norm(l, which, nw)
+            gm.set_norm(l, which, nw)
+    emb = oracle.quantize_weights_q8_0((rng.standard_normal((vocab, hidden)) * 0.02)
+                                       .astype(np.float32))
+    om.set_weight(0, 7, emb, vocab, hidden)
+    gm.set_weight(0, 7, emb, kb.DTYPE_Q8_0, vocab, hidden)
+    fn = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    om.set_norm(0, 2, fn)
+    gm.set_norm(0, 2, fn)
+
+    lens = [int(x) for x in rng.integers(1, 400, size=B)]
+    lens[0] = 1
+    NB = sum((c + bs - 1) // bs for c in lens) + 4
+    opool, gpool = oracle.KvPool(L, NB, bs, KH, hd), kb.KvPool(ctx, L, NB, bs, KH, hd)
+    perm = [int(b) for b in rng.permutation(NB)]
+    tables, used = [], 0
+    for c in lens:
+        need = (c + bs - 1) // bs
+        tables.append(perm[used:used + need])
+        used += need
+    for l in range(L):
+        hs, hk, hv = [], [], []
+        for s, c in enumerate(lens):
+            for t in range(c - 1):
+                slot = tables[s][t // bs] * bs + t % bs
+                k = rng.standard_normal(KH * hd).astype(np.float32)
+                v = rng.standard_normal(KH * hd).astype(np.float32)
+                opool.write_token(l, slot // bs, slot % bs, k, v)
+                hs.append(slot)
+                hk.append(k)
+                hv.append(v)
+        if hs:
+            gpool.write_slots(l, torch.from_numpy(np.array(hs, np.int32)).cuda(),
+                              torch.from_numpy(np.stack(hk)).cuda(),
+                              torch.from_numpy(np.stack(hv)).cuda(), len(hs))
+    st, maxb, padded = oracle.padded_decode_tables(bs, tables, lens)
+    assert st == 0
+    tokens = rng.integers(0, vocab, B).astype(np.uint32)
+    positions = np.array([c - 1 for c in lens], np.uint32)
+    slots = np.array([tables[s][(c - 1) // bs] * bs + (c - 1) % bs for s, c in enumerate(lens)],
+                     np.uint32)
+    st, ref = om.decode_step(opool, tokens, positions, slots, padded, lens, maxb)
+    assert st == 0
+    got = np.empty((B, vocab), np.float32)
+    gm.decode_step(gpool, tokens, positions, slots, padded, np.array(lens, np.uint32), maxb, got)
+    assert np.max(np.abs(got - ref)) <= 1e-2
+    assert [int(np.argmax(r)) for r in got] == [oracle.greedy_token(r) for r in ref]
+    # the K/V rows the step wrote are the bytes the CPU path stores
+    for s in range(B):
+        blk, off = int(slots[s]) // bs, int(slots[s]) % bs
+        _, o = opool.read_token(L - 1, blk, off)
+        gtok = gpool.read_token(L - 1, blk, off)
+        assert np.mean(gtok["k_q"] != o["k_q"]) <= 0.02  # activations differ by ~1e-5: rare ties
+        assert np.allclose(gtok["k_scale"], o["k_scale"], rtol=1e-4)
+    gm.destroy()
+    gpool.destroy()
+    ctx.close()
