@@ -29,11 +29,14 @@
 // or near-exact), and each 16-wide K step issues three MMAs: wh*xh + wl*xh + wh*xl. Only the
 // wl*xl term (2^-22) is dropped; products accumulate in f32 in TMEM. KANSO_ACT_Q8 (bit-exact int32 block sums) is not offered on this path: its
 // per-32 scales would force the accumulator out of TMEM every K=32.
+#include <cstdlib>
+
 #include "ctx.h"
 
 namespace kanso {
 
-constexpr int TC_THREADS = 256;
+constexpr int TC_PRODUCERS = 256;           // threads that copy, dequantise and run the epilogue
+constexpr int TC_THREADS = TC_PRODUCERS + 32;  // plus one warp that issues the MMAs
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
 constexpr int TC_A_PLANE = TC_TILE_N * TC_KC * 2;  // bytes of one f16 A term per stage (16 KB)
@@ -48,6 +51,7 @@ struct TcArgs {
   int bpr;           // blocks (Q8_0) or super-blocks (Q4_K) per row
   int ksplit;        // CTAs along K
   int stages_total;  // K / 64
+  int nstage_smem;   // shared-memory stages of the A/B tiles (2 or 3)
   int* status;
 };
 
@@ -156,17 +160,76 @@ constexpr int TC_FMT_Q4_K = 1;
 
 // Dequantise this thread's 32 weights of stage `s` into the A tile (core-matrix layout).
 // Q8_0: thread = (block tid / 128 of the two in the stage, row tid % 128).
-__device__ __forceinline__ void tc_dequant_q8_0(const TcArgs& a, int64_t n, int s, int tid,
-                                                uint8_t* As) {
-  const int blk = tid >> 7, row = tid & 127;
-  const uint8_t* p = a.w + (n * a.bpr + (int64_t)s * 2 + blk) * Q8_BYTES;
-  // the block is only 2-byte aligned: read the nine aligned words that cover it
-  const uintptr_t pa = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* al = reinterpret_cast<const uint32_t*>(pa & ~uintptr_t(3));
-  const uint32_t sh = (uint32_t)(pa & 3) * 8;  // 0 or 16
-  uint32_t r[9];
+// Raw weight bytes travel through a ring of TC_RAW_DEPTH shared-memory stages filled with
+// cp.async copies issued three stages ahead of their use, so the HBM latency is hidden
+// without holding registers. A raw stage keeps, per weight row, the bytes of that row's
+// 64 K-values: Q8_0 two blocks = 68 bytes (row stride 68: odd word stride, conflict-free);
+// Q4_K header + 32 nibble bytes = 48 bytes (row stride 80 for conflict-free 128-bit loads).
+constexpr int TC_RAW_DEPTH = 4;  // raw stages in flight: three ahead of the one in use
+constexpr int TC_RAW_ROW_Q8 = 68;
+constexpr int TC_RAW_ROW_Q4 = 80;
+constexpr int TC_RAW_STAGE = TC_TILE_N * TC_RAW_ROW_Q4;  // the larger of the two
+
+struct TcRaw {
+  uint32_t r[12];
+  uint32_t sh;
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16_cg(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// thread = (row tid / 2, half tid % 2) copies its part of the row's raw bytes of stage s
+__device__ __forceinline__ void tc_copy_raw_q8_0(const TcArgs& a, int64_t n_of_row, int s,
+                                                 int tid, uint32_t raw_stage) {
+  const int row = tid >> 1, half = tid & 1;
+  // 17 words per row (rows and stage offsets are 4-byte aligned): 9 + 8
+  const uint8_t* src = a.w + (n_of_row * a.bpr + (int64_t)s * 2) * Q8_BYTES + 36 * half;
+  const uint32_t dst = raw_stage + row * TC_RAW_ROW_Q8 + 36 * half;
 #pragma unroll
-  for (int k = 0; k < 9; ++k) r[k] = __ldg(al + k);
+  for (int k = 0; k < 8; ++k) cp_async4(dst + 4 * k, src + 4 * k);
+  if (half == 0) cp_async4(dst + 32, src + 32);
+}
+__device__ __forceinline__ void tc_copy_raw_q4_k(const TcArgs& a, int64_t n_of_row, int s,
+                                                 int tid, uint32_t raw_stage) {
+  const int row = tid >> 1, half = tid & 1;
+  const int sb = s >> 2, g = s & 3;
+  const uint8_t* p = a.w + (n_of_row * a.bpr + sb) * Q4K_BYTES;
+  const uint32_t dst = raw_stage + row * TC_RAW_ROW_Q4;
+  if (half == 0) {
+    cp_async16_cg(dst, p);                        // header
+    cp_async16_cg(dst + 16, p + 16 + 32 * g);     // nibble bytes 0..15 of the group
+  } else {
+    cp_async16_cg(dst + 32, p + 32 + 32 * g);     // nibble bytes 16..31
+  }
+}
+
+// thread = (block or nibble half tid / 128, row tid % 128) reads its raw bytes back
+__device__ __forceinline__ void tc_read_raw_q8_0(const uint8_t* raw_stage, int tid, TcRaw& raw) {
+  const int blk = tid >> 7, row = tid & 127;
+  const uint32_t off = row * TC_RAW_ROW_Q8 + blk * Q8_BYTES;  // 2-byte aligned
+  const uint32_t* al = reinterpret_cast<const uint32_t*>(raw_stage + (off & ~3u));
+  raw.sh = (off & 3u) * 8;  // 0 or 16
+#pragma unroll
+  for (int k = 0; k < 9; ++k) raw.r[k] = al[k];
+}
+__device__ __forceinline__ void tc_read_raw_q4_k(const uint8_t* raw_stage, int tid, TcRaw& raw) {
+  const int row = tid & 127;
+  const uint4* p = reinterpret_cast<const uint4*>(raw_stage + row * TC_RAW_ROW_Q4);
+  const uint4 hdr = p[0], qa = p[1], qb = p[2];
+  raw.r[0] = hdr.x; raw.r[1] = hdr.y; raw.r[2] = hdr.z; raw.r[3] = hdr.w;
+  raw.r[4] = qa.x; raw.r[5] = qa.y; raw.r[6] = qa.z; raw.r[7] = qa.w;
+  raw.r[8] = qb.x; raw.r[9] = qb.y; raw.r[10] = qb.z; raw.r[11] = qb.w;
+  raw.sh = 0;
+}
+
+__device__ __forceinline__ void tc_dequant_q8_0(const TcRaw& raw, int tid, uint8_t* As) {
+  const int blk = tid >> 7, row = tid & 127;
+  const uint32_t* r = raw.r;
+  const uint32_t sh = raw.sh;
   uint32_t v[9];  // the 34 bytes of the block, from its first byte
 #pragma unroll
   for (int k = 0; k < 8; ++k) v[k] = __funnelshift_r(r[k], r[k + 1], sh);
@@ -204,14 +267,12 @@ __device__ __forceinline__ void tc_dequant_q8_0(const TcArgs& a, int64_t n, int 
 // Q4_K: stage s = 64-weight group g = s % 4 of super-block s / 4; thread = (nibble half
 // tid / 128 -> sub-block 2g + half, row tid % 128). (d*sc)*q - dmin*m as src/quant/q4_k.rs:30-55,
 // then one rounding to f16.
-__device__ __forceinline__ void tc_dequant_q4_k(const TcArgs& a, int64_t n, int s, int tid,
-                                                uint8_t* As) {
+__device__ __forceinline__ void tc_dequant_q4_k(const TcRaw& raw, int s, int tid, uint8_t* As) {
   const int half = tid >> 7, row = tid & 127;
-  const int sb = s >> 2, g = s & 3;
-  const uint8_t* p = a.w + (n * a.bpr + sb) * Q4K_BYTES;
-  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(p));
-  const uint4 qa = __ldg(reinterpret_cast<const uint4*>(p + 16 + 32 * g));
-  const uint4 qb = __ldg(reinterpret_cast<const uint4*>(p + 32 + 32 * g));
+  const int g = s & 3;
+  const uint4 hdr = make_uint4(raw.r[0], raw.r[1], raw.r[2], raw.r[3]);
+  const uint4 qa = make_uint4(raw.r[4], raw.r[5], raw.r[6], raw.r[7]);
+  const uint4 qb = make_uint4(raw.r[8], raw.r[9], raw.r[10], raw.r[11]);
   const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
   uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
   unpack_scales_k4(hdr.y, hdr.z, hdr.w, sc_lo, sc_hi, mn_lo, mn_hi);
@@ -251,16 +312,22 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcArgs& a, int64_t n, int 
   }
 }
 
+// Warps 0-7 produce the tiles (copies, dequantisation, the epilogue); warp 8 only issues MMAs,
+// so building descriptors and issuing never delays the next stage's dequantisation.
 template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t b_plane = 8u * a.Mt * 16u;  // bytes of one term of the B tile of a stage
   const uint32_t b_stage = 2u * b_plane;
+  const int NS = a.nstage_smem;  // shared-memory stages of the A/B tiles (2 or 3)
   uint8_t* As = smem;
-  uint8_t* Bs = smem + 2 * TC_A_STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Bs + 2 * b_stage);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint8_t* Bs = smem + NS * TC_A_STAGE;
+  uint64_t* done = reinterpret_cast<uint64_t*>(Bs + NS * b_stage);  // [3] MMAs of a buffer retired
+  uint64_t* full = done + 3;                                        // [3] tiles of a buffer ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + 3);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* Raw = reinterpret_cast<uint8_t*>(done) + 64;  // 16-byte aligned
 
   const int64_t n0 = (int64_t)blockIdx.x * TC_TILE_N;
   const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
@@ -270,62 +337,123 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
   if (warp == 0) tmem_alloc(tmem_slot, ncols);
   if (tid == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&done[i], 1);
+      mbar_init(&full[i], TC_PRODUCERS);
+    }
+    *abort_flag = 0;
     mbar_fence_init();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
 
-  const int64_t n_row = min(n0 + (tid & 127), a.N - 1);  // rows past N re-read the last row
-  int failed = 0;
-  for (int s = s0; s < s1; ++s) {
-    const int it = s - s0, buf = it & 1;
-    if (it >= 2)  // the MMAs that read this buffer two stages ago must be done
-      failed = !mbar_wait_bounded(&bars[buf], (uint32_t)((it - 2) >> 1) & 1);
-    if (__syncthreads_or(failed)) {
-      failed = 1;
-      break;
+  if (warp < TC_PRODUCERS / 32) {
+    const int64_t n_copy = min(n0 + (tid >> 1), a.N - 1);  // rows past N re-read the last row
+    const uint32_t raw_base = smem_u32(Raw);
+    // one commit group per call, also when there is nothing left to copy, so that the
+    // wait_group arithmetic below holds at the ends of the K range
+    auto copy_b = [&](int s) {  // B tile of stage s -> buffer (s - s0) % NS
+      if (s < s1) {
+        const uint4* bsrc = reinterpret_cast<const uint4*>(a.xp) + (size_t)s * (b_stage / 16);
+        const uint32_t dst = smem_u32(Bs + ((s - s0) % NS) * b_stage);
+        for (uint32_t i = tid; i < b_stage / 16; i += TC_PRODUCERS)
+          cp_async16_cg(dst + 16u * i, bsrc + i);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto copy_raw = [&](int s) {  // raw weights of stage s -> raw slot (s - s0) % TC_RAW_DEPTH
+      if (s < s1) {
+        const uint32_t dst = raw_base + ((s - s0) % TC_RAW_DEPTH) * TC_RAW_STAGE;
+        if (FMT == TC_FMT_Q8_0)
+          tc_copy_raw_q8_0(a, n_copy, s, tid, dst);
+        else
+          tc_copy_raw_q4_k(a, n_copy, s, tid, dst);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // commit order in steady state: ..., B(s), raw(s+2), B(s+1), raw(s+3)
+    copy_raw(s0);
+    copy_raw(s0 + 1);
+    copy_b(s0);
+    copy_raw(s0 + 2);
+    for (int s = s0; s < s1; ++s) {
+      const int it = s - s0, buf = it % NS;
+      uint32_t failed = 0;
+      // the A/B buffer of stage s+1 was last read by the MMAs of stage s+1-NS
+      if (it + 1 >= NS)
+        failed = !mbar_wait_bounded(&done[(it + 1) % NS], (uint32_t)((it + 1 - NS) / NS) & 1);
+      copy_b(s + 1);
+      copy_raw(s + 3);
+      // all but the three newest groups have landed: B(s), raw(s) and raw(s+1)
+      asm volatile("cp.async.wait_group 3;" ::: "memory");
+      // producers' barrier: every producer's copies of this stage are visible; also the vote
+      uint32_t any_failed;
+      asm volatile(
+          "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, %2, q;\n"
+          "selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(any_failed)
+          : "r"(failed | *abort_flag), "n"(TC_PRODUCERS)
+          : "memory");
+      if (any_failed) {
+        *abort_flag = 1;
+        break;
+      }
+      uint8_t* Ab = As + buf * TC_A_STAGE;
+      TcRaw cur;
+      const uint8_t* rs = Raw + (it % TC_RAW_DEPTH) * TC_RAW_STAGE;
+      if (FMT == TC_FMT_Q8_0) {
+        tc_read_raw_q8_0(rs, tid, cur);
+        tc_dequant_q8_0(cur, tid, Ab);
+      } else {
+        tc_read_raw_q4_k(rs, tid, cur);
+        tc_dequant_q4_k(cur, s, tid, Ab);
+      }
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+      mbar_arrive(&full[buf]);
     }
-    uint8_t* Ab = As + buf * TC_A_STAGE;
-    uint8_t* Bb = Bs + buf * b_stage;
-    if (FMT == TC_FMT_Q8_0)
-      tc_dequant_q8_0(a, n_row, s, tid, Ab);
-    else
-      tc_dequant_q4_k(a, n_row, s, tid, Ab);
-    const uint4* bsrc = reinterpret_cast<const uint4*>(a.xp) + (size_t)s * (b_stage / 16);
-    for (uint32_t i = tid; i < b_stage / 16; i += TC_THREADS)
-      reinterpret_cast<uint4*>(Bb)[i] = __ldg(bsrc + i);
-    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else {
+   if (lane == 0) {
+    // the MMA issuer
+    const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
+    const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;  // per 16 k
+    for (int s = s0; s < s1; ++s) {
+      const int it = s - s0, buf = it % NS;
+      if (*abort_flag || !mbar_wait_bounded(&full[buf], (uint32_t)(it / NS) & 1)) {
+        *abort_flag = 1;
+        break;
+      }
       tc_fence_after();
-      const uint32_t a_addr = smem_u32(Ab), b_addr = smem_u32(Bb);
+      const uint32_t a_addr = smem_u32(As + buf * TC_A_STAGE);
+      const uint32_t b_addr = smem_u32(Bs + buf * b_stage);
+      const uint64_t ah0 = tc_smem_desc(a_addr, TC_TILE_N * 16, 128);
+      const uint64_t al0 = tc_smem_desc(a_addr + TC_A_PLANE, TC_TILE_N * 16, 128);
+      const uint64_t bh0 = tc_smem_desc(b_addr, a.Mt * 16, 128);
+      const uint64_t bl0 = tc_smem_desc(b_addr + b_plane, a.Mt * 16, 128);
 #pragma unroll
       for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
-        const uint32_t ao = j * 2 * (TC_TILE_N * 16), bo = j * 2 * (a.Mt * 16);
-        const uint64_t ah = tc_smem_desc(a_addr + ao, TC_TILE_N * 16, 128);
-        const uint64_t al = tc_smem_desc(a_addr + TC_A_PLANE + ao, TC_TILE_N * 16, 128);
-        const uint64_t bh = tc_smem_desc(b_addr + bo, a.Mt * 16, 128);
-        const uint64_t bl = tc_smem_desc(b_addr + b_plane + bo, a.Mt * 16, 128);
+        const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
+        const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
         tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
         tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
         tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
       }
-      tc_commit(&bars[buf]);
+      tc_commit(&done[buf]);
     }
+   }
+   __syncwarp();
   }
+  __syncthreads();
+  int failed = *abort_flag != 0;
   if (!failed && s1 > s0) {
     const int last = s1 - s0 - 1;
-    failed = !mbar_wait_bounded(&bars[last & 1], (uint32_t)(last >> 1) & 1);
+    failed = !mbar_wait_bounded(&done[last % NS], (uint32_t)(last / NS) & 1);
   }
   failed = __syncthreads_or(failed);
   tc_fence_after();
-  if (!failed && s1 > s0) {
+  if (!failed && s1 > s0 && warp < TC_PRODUCERS / 32) {
     // lane = weight row inside the tile, column = activation row
     const int q = warp & 3;
     const int64_t n = n0 + q * 32 + lane;
@@ -354,20 +482,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   if (warp == 0) tmem_dealloc(tmem_base, ncols);
 }
 
-// y[M,N] = x[M,K] @ W^T on the tensor cores; M in 9..256 per call (larger M is chunked by
+// y[M,N] = x[M,K] @ W^T on the tensor cores; M up to 128 per call (larger M is chunked by
 // the caller). Sets *handled = false when the shape is outside this kernel's range.
 int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
                   int64_t M, int64_t N, int64_t K, bool* handled) {
   *handled = false;
   const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
-  if (M < 1 || M > 256 || N < 1 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
+  if (M < 1 || M > 128 || N < 1 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
   if (dtype == KANSO_DTYPE_Q8_0 && (reinterpret_cast<uintptr_t>(w) & 3) != 0) return KANSO_OK;
   const int Mt = (int)((M + 15) / 16 * 16);
   const int stages_total = (int)(K / TC_KC);
   const int tiles_n = (int)((N + TC_TILE_N - 1) / TC_TILE_N);
   // split K until the grid covers the SMs about twice, keeping >= 4 stages per CTA
+  // Split K only when the row tiles alone would leave more than half of the SMs idle: the
+  // partial sums of a split are added with atomics (after a clear of y), which costs more
+  // than an under-filled grid does. At least 4 stages stay in every CTA.
   int ksplit = 1;
-  while (tiles_n * ksplit < 2 * ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
+  while (tiles_n * ksplit * 2 <= ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
   const size_t xp_bytes = 2 * (size_t)(K / 8) * Mt * 16;
   uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
   if (!scratch) return KANSO_ERR_DEVICE;
@@ -394,7 +525,16 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   a.ksplit = ksplit;
   a.stages_total = stages_total;
   a.status = ctx->dev_status;
-  const size_t smem = 2 * TC_A_STAGE + 2 * (size_t)(2 * 8 * Mt * 16) + 64;
+  const size_t per_stage = TC_A_STAGE + (size_t)(2 * 8 * Mt * 16);
+  const size_t fixed = 64 + (size_t)TC_RAW_DEPTH * TC_RAW_STAGE;
+  // two A/B stages when that lets two CTAs share an SM (more warps to hide latency), else
+  // three stages if they fit
+  const size_t half_sm = ((size_t)ctx->smem_optin - 2048) / 2;
+  if (2 * per_stage + fixed <= half_sm)
+    a.nstage_smem = 2;
+  else
+    a.nstage_smem = 3 * per_stage + fixed <= (size_t)ctx->smem_optin ? 3 : 2;
+  const size_t smem = a.nstage_smem * per_stage + fixed;
   auto kern = dtype == KANSO_DTYPE_Q8_0 ? gemm_tc_kernel<TC_FMT_Q8_0> : gemm_tc_kernel<TC_FMT_Q4_K>;
   static bool attr_set[2][16] = {};
   bool& done = attr_set[dtype == KANSO_DTYPE_Q8_0 ? 0 : 1][ctx->device & 15];

@@ -13,13 +13,14 @@ int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
 
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
-  // More than 8 activation rows: the tcgen05 GEMM, at most 256 rows per pass over the weights.
+  // More than 8 activation rows: the tcgen05 GEMM, at most 128 rows per pass over the weights
+  // (the A/B tiles of two stages plus the raw-byte ring fill one SM's shared memory).
   if (M > 8 && act_mode == KANSO_ACT_F32 && (dtype == KANSO_DTYPE_Q8_0 || dtype == KANSO_DTYPE_Q4_K) &&
       N > 0 && K > 0 && w && x && y && aligned16(x)) {
     bool all = true;
-    for (int64_t m0 = 0; m0 < M && all; m0 += 256) {
+    for (int64_t m0 = 0; m0 < M && all; m0 += 128) {
       bool handled = false;
-      int32_t st = tc_matmul(ctx, dtype, w, x + m0 * K, y + m0 * N, M - m0 < 256 ? M - m0 : 256, N,
+      int32_t st = tc_matmul(ctx, dtype, w, x + m0 * K, y + m0 * N, M - m0 < 128 ? M - m0 : 128, N,
                              K, &handled);
       if (st != KANSO_OK) return st;
       if (!handled) all = false;
