@@ -35,7 +35,7 @@
 
 namespace kanso {
 
-constexpr int TC_PRODUCERS = 256;           // threads that copy, dequantise and run the epilogue
+constexpr int TC_PRODUCERS = 512;           // threads that copy, dequantise and run the epilogue
 constexpr int TC_THREADS = TC_PRODUCERS + 32;  // plus one warp that issues the MMAs
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
@@ -158,8 +158,6 @@ __host__ __device__ inline uint32_t tc_idesc_f16(int m, int n) {
 constexpr int TC_FMT_Q8_0 = 0;
 constexpr int TC_FMT_Q4_K = 1;
 
-// Dequantise this thread's 32 weights of stage `s` into the A tile (core-matrix layout).
-// Q8_0: thread = (block tid / 128 of the two in the stage, row tid % 128).
 // Raw weight bytes travel through a ring of TC_RAW_DEPTH shared-memory stages filled with
 // cp.async copies issued three stages ahead of their use, so the HBM latency is hidden
 // without holding registers. A raw stage keeps, per weight row, the bytes of that row's
@@ -170,11 +168,6 @@ constexpr int TC_RAW_ROW_Q8 = 68;
 constexpr int TC_RAW_ROW_Q4 = 80;
 constexpr int TC_RAW_STAGE = TC_TILE_N * TC_RAW_ROW_Q4;  // the larger of the two
 
-struct TcRaw {
-  uint32_t r[12];
-  uint32_t sh;
-};
-
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -182,67 +175,72 @@ __device__ __forceinline__ void cp_async16_cg(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-// thread = (row tid / 2, half tid % 2) copies its part of the row's raw bytes of stage s
-__device__ __forceinline__ void tc_copy_raw_q8_0(const TcArgs& a, int64_t n_of_row, int s,
-                                                 int tid, uint32_t raw_stage) {
-  const int row = tid >> 1, half = tid & 1;
-  // 17 words per row (rows and stage offsets are 4-byte aligned): 9 + 8
-  const uint8_t* src = a.w + (n_of_row * a.bpr + (int64_t)s * 2) * Q8_BYTES + 36 * half;
-  const uint32_t dst = raw_stage + row * TC_RAW_ROW_Q8 + 36 * half;
+// Per-thread source and destination offsets of the raw-byte copies, fixed for the whole K loop.
+// Q8_0: the stage's 128 rows x 17 words are dealt to the threads in flat order, so the lanes
+// of a warp copy consecutive words of two or three rows (few memory lines per instruction).
+// Q4_K: threads 0..383 = (row tid / 3, part tid % 3): header, nibble bytes 0..15, 16..31.
+template <int FMT>
+struct TcRawCopy {
+  static constexpr int kPerThread =
+      FMT == TC_FMT_Q8_0 ? (TC_TILE_N * 17 + TC_PRODUCERS - 1) / TC_PRODUCERS : 1;
+  const uint8_t* src[kPerThread];
+  uint32_t dst[kPerThread];
+  bool on[kPerThread];
+  int part;
+
+  __device__ __forceinline__ void init(const TcArgs& a, int64_t n0, int tid) {
+    if (FMT == TC_FMT_Q8_0) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) cp_async4(dst + 4 * k, src + 4 * k);
-  if (half == 0) cp_async4(dst + 32, src + 32);
-}
-__device__ __forceinline__ void tc_copy_raw_q4_k(const TcArgs& a, int64_t n_of_row, int s,
-                                                 int tid, uint32_t raw_stage) {
-  const int row = tid >> 1, half = tid & 1;
-  const int sb = s >> 2, g = s & 3;
-  const uint8_t* p = a.w + (n_of_row * a.bpr + sb) * Q4K_BYTES;
-  const uint32_t dst = raw_stage + row * TC_RAW_ROW_Q4;
-  if (half == 0) {
-    cp_async16_cg(dst, p);                        // header
-    cp_async16_cg(dst + 16, p + 16 + 32 * g);     // nibble bytes 0..15 of the group
-  } else {
-    cp_async16_cg(dst + 32, p + 32 + 32 * g);     // nibble bytes 16..31
+      for (int k = 0; k < kPerThread; ++k) {
+        const int idx = tid + k * TC_PRODUCERS;
+        on[k] = idx < TC_TILE_N * 17;
+        const int row = min(idx / 17, TC_TILE_N - 1), word = idx - 17 * (idx / 17);
+        const int64_t n = min(n0 + row, a.N - 1);  // rows past N re-read the last row
+        src[k] = a.w + n * a.bpr * Q8_BYTES + 4 * word;
+        dst[k] = row * TC_RAW_ROW_Q8 + 4 * word;
+      }
+    } else {
+      on[0] = tid < 3 * TC_TILE_N;
+      const int row = min(tid / 3, TC_TILE_N - 1);
+      part = tid - 3 * (tid / 3);
+      src[0] = a.w + min(n0 + row, a.N - 1) * a.bpr * Q4K_BYTES;
+      dst[0] = row * TC_RAW_ROW_Q4 + 16 * part;
+    }
   }
-}
-
-// thread = (block or nibble half tid / 128, row tid % 128) reads its raw bytes back
-__device__ __forceinline__ void tc_read_raw_q8_0(const uint8_t* raw_stage, int tid, TcRaw& raw) {
-  const int blk = tid >> 7, row = tid & 127;
-  const uint32_t off = row * TC_RAW_ROW_Q8 + blk * Q8_BYTES;  // 2-byte aligned
-  const uint32_t* al = reinterpret_cast<const uint32_t*>(raw_stage + (off & ~3u));
-  raw.sh = (off & 3u) * 8;  // 0 or 16
+  __device__ __forceinline__ void issue(int s, uint32_t raw_stage) const {
+    if (FMT == TC_FMT_Q8_0) {
 #pragma unroll
-  for (int k = 0; k < 9; ++k) raw.r[k] = al[k];
-}
-__device__ __forceinline__ void tc_read_raw_q4_k(const uint8_t* raw_stage, int tid, TcRaw& raw) {
-  const int row = tid & 127;
-  const uint4* p = reinterpret_cast<const uint4*>(raw_stage + row * TC_RAW_ROW_Q4);
-  const uint4 hdr = p[0], qa = p[1], qb = p[2];
-  raw.r[0] = hdr.x; raw.r[1] = hdr.y; raw.r[2] = hdr.z; raw.r[3] = hdr.w;
-  raw.r[4] = qa.x; raw.r[5] = qa.y; raw.r[6] = qa.z; raw.r[7] = qa.w;
-  raw.r[8] = qb.x; raw.r[9] = qb.y; raw.r[10] = qb.z; raw.r[11] = qb.w;
-  raw.sh = 0;
-}
+      for (int k = 0; k < kPerThread; ++k)
+        if (on[k]) cp_async4(raw_stage + dst[k], src[k] + (int64_t)s * (2 * Q8_BYTES));
+    } else if (on[0]) {
+      const uint8_t* p = src[0] + (int64_t)(s >> 2) * Q4K_BYTES;
+      cp_async16_cg(raw_stage + dst[0], part == 0 ? p : p + 32 * (s & 3) + 16 * part);
+    }
+  }
+};
 
-__device__ __forceinline__ void tc_dequant_q8_0(const TcRaw& raw, int tid, uint8_t* As) {
-  const int blk = tid >> 7, row = tid & 127;
-  const uint32_t* r = raw.r;
-  const uint32_t sh = raw.sh;
-  uint32_t v[9];  // the 34 bytes of the block, from its first byte
+// Dequantise this thread's 16 weights of the stage into the A tile (core-matrix layout):
+// two chunks of 8 k-values, each one 16-byte row of a core matrix, in a hi and a lo plane.
+// Q8_0: thread = (block tid / 256 of the two in the stage, half block (tid / 128) % 2, row).
+__device__ __forceinline__ void tc_dequant_q8_0(const uint8_t* raw_stage, int tid, uint8_t* As) {
+  const int blk = tid >> 8, hb = (tid >> 7) & 1, row = tid & 127;
+  const uint32_t off = row * TC_RAW_ROW_Q8 + blk * Q8_BYTES;  // of the block; 2-byte aligned
+  const __half d = *reinterpret_cast<const __half*>(raw_stage + off);
+  const uint32_t qoff = off + 2 + 16 * hb;  // 16 int8 values, 2-byte aligned
+  const uint32_t* al = reinterpret_cast<const uint32_t*>(raw_stage + (qoff & ~3u));
+  const uint32_t sh = (qoff & 3u) * 8;  // 0 or 16, the same for the whole warp
+  uint32_t r[5];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) v[k] = __funnelshift_r(r[k], r[k + 1], sh);
-  v[8] = r[8] >> sh;
-  const __half d = __ushort_as_half((unsigned short)(v[0] & 0xFFFFu));
+  for (int k = 0; k < 4; ++k) r[k] = al[k];
+  r[4] = sh ? al[4] : 0u;
   const __half2 d2 = __half2half2(d);
   const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128, exact in f16
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {  // chunk of 8 weights = two words of int8
+  for (int c = 0; c < 2; ++c) {  // chunk of 8 weights = two words of int8
     uint32_t out[4], rem[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint32_t q = __funnelshift_r(v[2 * c + h], v[2 * c + h + 1], 16) ^ 0x80808080u;
+      const uint32_t q = __funnelshift_r(r[2 * c + h], r[2 * c + h + 1], sh) ^ 0x80808080u;
       // 0x6400 | byte = 1024 + (q + 128) as f16, exactly
       uint32_t p01 = __byte_perm(q, 0x64646464u, 0x4140);
       uint32_t p23 = __byte_perm(q, 0x64646464u, 0x4342);
@@ -256,7 +254,7 @@ __device__ __forceinline__ void tc_dequant_q8_0(const TcRaw& raw, int tid, uint8
       rem[2 * h] = *reinterpret_cast<uint32_t*>(&l01);
       rem[2 * h + 1] = *reinterpret_cast<uint32_t*>(&l23);
     }
-    const int kc = blk * 4 + c;  // chunk of 8 k-values within the stage
+    const int kc = blk * 4 + hb * 2 + c;  // chunk of 8 k-values within the stage
     *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
         make_uint4(out[0], out[1], out[2], out[3]);
     *reinterpret_cast<uint4*>(As + TC_A_PLANE + kc * (TC_TILE_N * 16) + row * 16) =
@@ -265,14 +263,14 @@ __device__ __forceinline__ void tc_dequant_q8_0(const TcRaw& raw, int tid, uint8
 }
 
 // Q4_K: stage s = 64-weight group g = s % 4 of super-block s / 4; thread = (nibble half
-// tid / 128 -> sub-block 2g + half, row tid % 128). (d*sc)*q - dmin*m as src/quant/q4_k.rs:30-55,
-// then one rounding to f16.
-__device__ __forceinline__ void tc_dequant_q4_k(const TcRaw& raw, int s, int tid, uint8_t* As) {
-  const int half = tid >> 7, row = tid & 127;
+// tid / 256 -> sub-block 2g + half, byte half (tid / 128) % 2 -> 16 of the 32 nibble bytes, row).
+// (d*sc)*q - dmin*m as src/quant/q4_k.rs:30-55, then split into two f16 terms.
+__device__ __forceinline__ void tc_dequant_q4_k(const uint8_t* raw_stage, int s, int tid,
+                                                uint8_t* As) {
+  const int half = tid >> 8, part = (tid >> 7) & 1, row = tid & 127;
   const int g = s & 3;
-  const uint4 hdr = make_uint4(raw.r[0], raw.r[1], raw.r[2], raw.r[3]);
-  const uint4 qa = make_uint4(raw.r[4], raw.r[5], raw.r[6], raw.r[7]);
-  const uint4 qb = make_uint4(raw.r[8], raw.r[9], raw.r[10], raw.r[11]);
+  const uint4* p = reinterpret_cast<const uint4*>(raw_stage + row * TC_RAW_ROW_Q4);
+  const uint4 hdr = p[0], qv = p[1 + part];
   const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
   uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
   unpack_scales_k4(hdr.y, hdr.z, hdr.w, sc_lo, sc_hi, mn_lo, mn_hi);
@@ -280,10 +278,10 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcRaw& raw, int s, int tid
   const uint32_t scw = j < 4 ? sc_lo : sc_hi, mnw = j < 4 ? mn_lo : mn_hi;
   const float d1 = __fmul_rn(d, (float)((scw >> (8 * (j & 3))) & 0xFF));
   const float m1 = __fmul_rn(dmin, (float)((mnw >> (8 * (j & 3))) & 0xFF));
-  const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+  const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
   const int sh0 = 4 * half;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
     uint32_t out[4], rem[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -304,7 +302,8 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcRaw& raw, int s, int tid
       rem[2 * h] = *reinterpret_cast<uint32_t*>(&l01);
       rem[2 * h + 1] = *reinterpret_cast<uint32_t*>(&l23);
     }
-    const int kc = half * 4 + c;  // low nibbles: k 0..31 of the group, high nibbles: 32..63
+    // low nibbles: k 0..31 of the group, high nibbles: 32..63
+    const int kc = half * 4 + part * 2 + c;
     *reinterpret_cast<uint4*>(As + kc * (TC_TILE_N * 16) + row * 16) =
         make_uint4(out[0], out[1], out[2], out[3]);
     *reinterpret_cast<uint4*>(As + TC_A_PLANE + kc * (TC_TILE_N * 16) + row * 16) =
@@ -312,8 +311,10 @@ __device__ __forceinline__ void tc_dequant_q4_k(const TcRaw& raw, int s, int tid
   }
 }
 
-// Warps 0-7 produce the tiles (copies, dequantisation, the epilogue); warp 8 only issues MMAs,
-// so building descriptors and issuing never delays the next stage's dequantisation.
+// Warps 0-15 produce the A tiles (raw-byte copies, dequantisation) and run the epilogue; warp 16
+// fetches the B tiles with one bulk copy per stage and issues the MMAs, so building descriptors
+// and issuing never delays the next stage's dequantisation. Buffer indices and mbarrier
+// parities are carried as counters (no division in the loop).
 template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -324,10 +325,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   uint8_t* As = smem;
   uint8_t* Bs = smem + NS * TC_A_STAGE;
   uint64_t* done = reinterpret_cast<uint64_t*>(Bs + NS * b_stage);  // [3] MMAs of a buffer retired
-  uint64_t* full = done + 3;                                        // [3] tiles of a buffer ready
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + 3);
+  uint64_t* full = done + 3;                                        // [3] A tile of a buffer ready
+  uint64_t* bfull = full + 3;                                       // [3] B tile of a buffer landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bfull + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint8_t* Raw = reinterpret_cast<uint8_t*>(done) + 64;  // 16-byte aligned
+  uint8_t* Raw = reinterpret_cast<uint8_t*>(done) + 96;  // 16-byte aligned
 
   const int64_t n0 = (int64_t)blockIdx.x * TC_TILE_N;
   const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
@@ -339,7 +341,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(&done[i], 1);
-      mbar_init(&full[i], TC_PRODUCERS);
+      mbar_init(&full[i], TC_PRODUCERS / 32);  // one arrival per producer warp
+      mbar_init(&bfull[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -350,100 +353,98 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < TC_PRODUCERS / 32) {
-    const int64_t n_copy = min(n0 + (tid >> 1), a.N - 1);  // rows past N re-read the last row
+    TcRawCopy<FMT> raw_copy;
+    raw_copy.init(a, n0, tid);
     const uint32_t raw_base = smem_u32(Raw);
     // one commit group per call, also when there is nothing left to copy, so that the
-    // wait_group arithmetic below holds at the ends of the K range
-    auto copy_b = [&](int s) {  // B tile of stage s -> buffer (s - s0) % NS
-      if (s < s1) {
-        const uint4* bsrc = reinterpret_cast<const uint4*>(a.xp) + (size_t)s * (b_stage / 16);
-        const uint32_t dst = smem_u32(Bs + ((s - s0) % NS) * b_stage);
-        for (uint32_t i = tid; i < b_stage / 16; i += TC_PRODUCERS)
-          cp_async16_cg(dst + 16u * i, bsrc + i);
-      }
+    // wait_group arithmetic below holds at the end of the K range
+    auto copy_raw = [&](int s, int slot) {
+      if (s < s1) raw_copy.issue(s, raw_base + slot * TC_RAW_STAGE);
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto copy_raw = [&](int s) {  // raw weights of stage s -> raw slot (s - s0) % TC_RAW_DEPTH
-      if (s < s1) {
-        const uint32_t dst = raw_base + ((s - s0) % TC_RAW_DEPTH) * TC_RAW_STAGE;
-        if (FMT == TC_FMT_Q8_0)
-          tc_copy_raw_q8_0(a, n_copy, s, tid, dst);
-        else
-          tc_copy_raw_q4_k(a, n_copy, s, tid, dst);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    // commit order in steady state: ..., B(s), raw(s+2), B(s+1), raw(s+3)
-    copy_raw(s0);
-    copy_raw(s0 + 1);
-    copy_b(s0);
-    copy_raw(s0 + 2);
+    copy_raw(s0, 0);
+    copy_raw(s0 + 1, 1);
+    copy_raw(s0 + 2, 2);
+    int buf = 0;             // A buffer of this stage
+    uint32_t reuse_par = 1;  // parity of done[buf] for the previous use of the buffer
     for (int s = s0; s < s1; ++s) {
-      const int it = s - s0, buf = it % NS;
-      uint32_t failed = 0;
-      // the A/B buffer of stage s+1 was last read by the MMAs of stage s+1-NS
-      if (it + 1 >= NS)
-        failed = !mbar_wait_bounded(&done[(it + 1) % NS], (uint32_t)((it + 1 - NS) / NS) & 1);
-      copy_b(s + 1);
-      copy_raw(s + 3);
-      // all but the three newest groups have landed: B(s), raw(s) and raw(s+1)
+      const int it = s - s0;
+      copy_raw(s + 3, (it + 3) & (TC_RAW_DEPTH - 1));
+      // the A buffer of this stage was last read by the MMAs of stage s - NS
+      if (it >= NS && !mbar_wait_bounded(&done[buf], reuse_par)) *abort_flag = 1;
+      // all but the three newest groups have landed: raw(s) is in shared memory
       asm volatile("cp.async.wait_group 3;" ::: "memory");
-      // producers' barrier: every producer's copies of this stage are visible; also the vote
-      uint32_t any_failed;
-      asm volatile(
-          "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, %2, q;\n"
-          "selp.u32 %0, 1, 0, p;\n}\n"
-          : "=r"(any_failed)
-          : "r"(failed | *abort_flag), "n"(TC_PRODUCERS)
-          : "memory");
-      if (any_failed) {
-        *abort_flag = 1;
-        break;
-      }
+      // producers' barrier: every producer's copies of this stage are visible to all
+      asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+      if (*abort_flag) break;
       uint8_t* Ab = As + buf * TC_A_STAGE;
-      TcRaw cur;
-      const uint8_t* rs = Raw + (it % TC_RAW_DEPTH) * TC_RAW_STAGE;
-      if (FMT == TC_FMT_Q8_0) {
-        tc_read_raw_q8_0(rs, tid, cur);
-        tc_dequant_q8_0(cur, tid, Ab);
-      } else {
-        tc_read_raw_q4_k(rs, tid, cur);
-        tc_dequant_q4_k(cur, s, tid, Ab);
-      }
+      const uint8_t* rs = Raw + (it & (TC_RAW_DEPTH - 1)) * TC_RAW_STAGE;
+      if (FMT == TC_FMT_Q8_0)
+        tc_dequant_q8_0(rs, tid, Ab);
+      else
+        tc_dequant_q4_k(rs, s, tid, Ab);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-      mbar_arrive(&full[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[buf]);
+      if (++buf == NS) {
+        buf = 0;
+        reuse_par ^= 1;
+      }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else {
-   if (lane == 0) {
-    // the MMA issuer
-    const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
-    const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;  // per 16 k
-    for (int s = s0; s < s1; ++s) {
-      const int it = s - s0, buf = it % NS;
-      if (*abort_flag || !mbar_wait_bounded(&full[buf], (uint32_t)(it / NS) & 1)) {
-        *abort_flag = 1;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t a_addr = smem_u32(As + buf * TC_A_STAGE);
-      const uint32_t b_addr = smem_u32(Bs + buf * b_stage);
-      const uint64_t ah0 = tc_smem_desc(a_addr, TC_TILE_N * 16, 128);
-      const uint64_t al0 = tc_smem_desc(a_addr + TC_A_PLANE, TC_TILE_N * 16, 128);
-      const uint64_t bh0 = tc_smem_desc(b_addr, a.Mt * 16, 128);
-      const uint64_t bl0 = tc_smem_desc(b_addr + b_plane, a.Mt * 16, 128);
+    if (lane == 0) {
+      // B tiles by bulk copy, then the MMAs
+      const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
+      const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;  // per 16 k
+      const uint8_t* bsrc = reinterpret_cast<const uint8_t*>(a.xp);
+      auto copy_b = [&](int s, int b) {
+        mbar_arrive_expect_tx(&bfull[b], b_stage);
+        bulk_g2s(Bs + b * b_stage, bsrc + (size_t)s * b_stage, b_stage, &bfull[b]);
+      };
+      for (int i = 0; i < NS - 1 && s0 + i < s1; ++i) copy_b(s0 + i, i);
+      int buf = 0, prev = NS - 1;  // prev = buffer of stage s - 1 = buffer of stage s + NS - 1
+      uint32_t par = 0, prev_par = 1;
+      for (int s = s0; s < s1; ++s) {
+        const int it = s - s0;
+        if (!mbar_wait_bounded(&full[buf], par) || !mbar_wait_bounded(&bfull[buf], par)) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(As + buf * TC_A_STAGE);
+        const uint32_t b_addr = smem_u32(Bs + buf * b_stage);
+        const uint64_t ah0 = tc_smem_desc(a_addr, TC_TILE_N * 16, 128);
+        const uint64_t al0 = tc_smem_desc(a_addr + TC_A_PLANE, TC_TILE_N * 16, 128);
+        const uint64_t bh0 = tc_smem_desc(b_addr, a.Mt * 16, 128);
+        const uint64_t bl0 = tc_smem_desc(b_addr + b_plane, a.Mt * 16, 128);
 #pragma unroll
-      for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
-        const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
-        const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
-        tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
-        tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
-        tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
+        for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
+          const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
+          const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
+          tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
+          tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
+          tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
+        }
+        tc_commit(&done[buf]);
+        // B of stage s+NS-1 goes where the MMAs of stage s-1 read: wait for those (issued one
+        // iteration ago; the MMAs just issued keep the tensor pipe busy meanwhile)
+        if (s + NS - 1 < s1) {
+          if (it >= 1 && !mbar_wait_bounded(&done[prev], prev_par)) {
+            *abort_flag = 1;
+            break;
+          }
+          copy_b(s + NS - 1, prev);
+        }
+        prev = buf;
+        prev_par = par;
+        if (++buf == NS) {
+          buf = 0;
+          par ^= 1;
+        }
       }
-      tc_commit(&done[buf]);
     }
-   }
-   __syncwarp();
+    __syncwarp();
   }
   __syncthreads();
   int failed = *abort_flag != 0;
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     // lane = weight row inside the tile, column = activation row
     const int q = warp & 3;
     const int64_t n = n0 + q * 32 + lane;
-    for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += 2) {
+    for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TC_PRODUCERS / 128) {
       uint32_t r[16];
       tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
       if (n < a.N) {
@@ -526,7 +527,7 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   a.stages_total = stages_total;
   a.status = ctx->dev_status;
   const size_t per_stage = TC_A_STAGE + (size_t)(2 * 8 * Mt * 16);
-  const size_t fixed = 64 + (size_t)TC_RAW_DEPTH * TC_RAW_STAGE;
+  const size_t fixed = 96 + (size_t)TC_RAW_DEPTH * TC_RAW_STAGE;
   // two A/B stages when that lets two CTAs share an SM (more warps to hide latency), else
   // three stages if they fit
   const size_t half_sm = ((size_t)ctx->smem_optin - 2048) / 2;
