@@ -115,6 +115,10 @@ int32_t kanso_cuda_ctx_create(int32_t device, void* stream, kanso_cuda_ctx** out
   }
   e = cudaMalloc(&ctx->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, sizeof(int));
+  if (e == cudaSuccess)
+    e = cudaMalloc(&ctx->pa_tickets, sizeof(uint32_t) * kanso_cuda_ctx::kPaTickets);
+  if (e == cudaSuccess)
+    e = cudaMemset(ctx->pa_tickets, 0, sizeof(uint32_t) * kanso_cuda_ctx::kPaTickets);
   if (e != cudaSuccess) {
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -132,6 +136,7 @@ int32_t kanso_cuda_ctx_destroy(kanso_cuda_ctx* ctx) {
   if (ctx->stage_dev) cudaFree(ctx->stage_dev);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->pa_tickets) cudaFree(ctx->pa_tickets);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return KANSO_OK;
@@ -145,6 +150,8 @@ int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx) {
                  "status word read");
   if (st != 0) {
     cudaMemset(ctx->dev_status, 0, sizeof(int));
+    // a kernel that gave up may have left attention tickets taken
+    cudaMemset(ctx->pa_tickets, 0, sizeof(uint32_t) * kanso_cuda_ctx::kPaTickets);
     if (st & DEV_WAIT_TIMEOUT)
       return fail(ctx, KANSO_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word %d)", st);
     return fail(ctx, KANSO_ERR_SHAPE,

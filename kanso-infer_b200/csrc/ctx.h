@@ -14,6 +14,10 @@ struct kanso_cuda_ctx {
   int sm_count = 0;
   int smem_optin = 0;      // max dynamic shared memory per block (opt-in), bytes
   int* dev_status = nullptr;  // one int on the device, OR of kanso::DevStatus
+  // arrival counters of the split-context attention (one per sequence and KV head); all zero
+  // between calls: the CTA that takes the last ticket of a counter resets it
+  uint32_t* pa_tickets = nullptr;
+  static constexpr uint32_t kPaTickets = 16384;
   uint64_t launches = 0;
   // weight buffers are never written by work enqueued before a matmul on this stream, so a
   // matmul may start fetching weights while the kernel before it is still running

@@ -608,6 +608,11 @@ static int32_t dispatch_m(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
 // Fused decode-step matmul on Q8_0 weights, at most 8 activation rows: up to three matrices
 // over the same activations, rmsnorm folded into the activation staging, silu(x)*x2 as the
 // activations, residual added to the result. Declared in glue.cuh.
+int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
+                      const int64_t* rows, const float* x, const float* x2, const float* norm_w,
+                      float eps, const float* resid, int64_t K, int M, int32_t act_mode,
+                      bool* handled);
+
 int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
                           const int64_t* rows, const float* x, const float* x2,
                           const float* norm_w, float eps, const float* resid, int64_t K, int M,
@@ -617,6 +622,13 @@ int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, f
                 (long long)K);
   if (resid && nseg != 1)
     return fail(ctx, KANSO_ERR_SHAPE, "fused matmul: a residual needs a single matrix");
+  {
+    // the tensor-core kernel takes the shapes it covers (K a multiple of 64, at most 4096)
+    bool handled = false;
+    int32_t st = q8_mma_matmul(ctx, nseg, w, y, rows, x, x2, norm_w, eps, resid, K, M, act_mode,
+                               &handled);
+    if (st != KANSO_OK || handled) return st;
+  }
   StreamCall c;
   c.nseg = nseg;
   for (int i = 0; i < nseg; ++i) {

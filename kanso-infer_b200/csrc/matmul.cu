@@ -11,6 +11,11 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
 int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y, int64_t M,
                           int64_t N, int64_t K, bool* handled);
 
+int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
+                      const int64_t* rows, const float* x, const float* x2, const float* norm_w,
+                      float eps, const float* resid, int64_t K, int M, int32_t act_mode,
+                      bool* handled);
+
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
   // More than 8 activation rows: the tcgen05 GEMM, at most 128 rows per pass over the weights
@@ -35,6 +40,22 @@ int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const
       bool handled = false;
       int32_t st = q4k_direct_matmul(ctx, w, x + m0 * K, y + m0 * N, M - m0 < 8 ? M - m0 : 8, N,
                                      K, &handled);
+      if (st != KANSO_OK) return st;
+      if (!handled) all = false;
+    }
+    if (all) return KANSO_OK;
+  }
+  if (dtype == KANSO_DTYPE_Q8_0 && (act_mode == KANSO_ACT_F32 || act_mode == KANSO_ACT_Q8) &&
+      K > 0 && M > 0 && N > 0 && w && x && y) {
+    // int8 tensor-core GEMV, at most 8 activation rows per pass over the weights
+    bool all = true;
+    for (int64_t m0 = 0; m0 < M && all; m0 += 8) {
+      bool handled = false;
+      const void* w1[1] = {w};
+      float* y1[1] = {y + m0 * N};
+      const int64_t r1[1] = {N};
+      int32_t st = q8_mma_matmul(ctx, 1, w1, y1, r1, x + m0 * K, nullptr, nullptr, 0.f, nullptr, K,
+                                 (int)(M - m0 < 8 ? M - m0 : 8), act_mode, &handled);
       if (st != KANSO_OK) return st;
       if (!handled) all = false;
     }

@@ -11,10 +11,13 @@
 //     packed bytes; the token's f32 K scale, the query scale and the softmax
 //     scale multiply the int32 sum once.
 //   * online softmax inside the partition (max, exp, sum) in shared memory.
-//   * PV: threads tile (dim word, token slice); V bytes are widened with one
+//   * PV: threads tile (8-dim word, token slice); V bytes are widened with one
 //     byte-permute each and accumulated in f32 with weight p * v_scale.
 //   Emits the unnormalised accumulator and (max, sum) per partition.
-// Stage 2 merges the partitions: out = sum acc_p e^{m_p-M} / sum l_p e^{m_p-M}.
+// Stage 2 merges the partitions: out = sum acc_p e^{m_p-M} / sum l_p e^{m_p-M}. With a ticket
+// array the merge runs inside stage 1, in the CTA that finishes last for its (sequence, kv head):
+// every CTA publishes its partials, fences, and takes a ticket; the one that draws the last
+// ticket reads all partials back. Nothing waits on anything, so there is no spin to bound.
 #include "glue.cuh"
 #include "kv_pool.h"
 
@@ -36,6 +39,7 @@ struct PaArgs {
   uint32_t num_heads, max_blocks, part_tokens, num_parts;
   float scale;
   int* status;
+  uint32_t* tickets;  // [seq][kv head], zero between calls; nullptr = separate stage-2 launch
 };
 
 __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
@@ -53,6 +57,11 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   const uint32_t part = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const uint32_t ctx = a.lens[seq];
   const uint32_t t0 = part * a.part_tokens;
+  if (ctx == 0 && a.tickets && part == 0) {
+    // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
+    float* o = a.out + ((size_t)seq * a.num_heads + (size_t)kvh * G) * hd;
+    for (uint32_t e = threadIdx.x; e < G * hd; e += PA_THREADS) o[e] = 0.f;
+  }
   if (t0 >= ctx) return;
   const uint32_t n = min(a.part_tokens, ctx - t0);
   const int tid = threadIdx.x;
@@ -64,7 +73,8 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   uint32_t* blk = reinterpret_cast<uint32_t*>(qd + PA_MAX_GROUP);  // [part_tokens/bs + 1]
   const uint32_t nblk_part = ((a.part_tokens + bs - 1) / bs + 4) & ~3u;
   float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
-  float* red = prob + ((G * a.part_tokens + 3) & ~3u);       // PV scratch, 16-byte aligned
+  float* vscs = prob + ((G * a.part_tokens + 3) & ~3u);      // [part_tokens] V scales
+  float* red = vscs + ((a.part_tokens + 3) & ~3u);           // PV scratch, 16-byte aligned
   __shared__ float s_red[32];
 
   // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
@@ -102,6 +112,30 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   __syncthreads();
   const uint32_t first_blk = t0 / bs;
 
+  // PV tiling: thread = (8 dims = one 64-bit word c of the V row, token slice). The loads of a
+  // thread's first four tokens are issued here, before the QK phase, so that short partitions
+  // pay one trip to memory for K and V together; later groups of four are loaded one group
+  // ahead of their use.
+  const uint32_t dwords = hd / 8;
+  const uint32_t nslice = PA_THREADS / dwords;  // hd in {16..256} -> dwords in {2..32}
+  const uint32_t c = tid % dwords, slice = tid / dwords;
+  auto load_v = [&](uint32_t i0, uint2 (&vw)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t i = i0 + j * nslice;
+      if (i < n) {
+        const uint32_t t = t0 + i;
+        const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
+        vw[j] = __ldg(reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(t % bs) * hd) +
+                      c);
+      } else {
+        vw[j] = make_uint2(0u, 0u);
+      }
+    }
+  };
+  uint2 vcur[4];
+  load_v(slice, vcur);
+
   // --- QK: one thread per token
   float lmax[G];
 #pragma unroll
@@ -112,23 +146,34 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
     const uint32_t off = t % bs;
     const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
     const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
+    vscs[i] = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
     int ih[G], il[G];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) ih[gq] = il[gq] = 0;
-    for (uint32_t c = 0; c < hd / 16; ++c) {
-      const uint4 kw = __ldg(krow + c);
+    const uint32_t nchunk = hd / 16;
+    for (uint32_t c0 = 0; c0 < nchunk; c0 += 4) {
+      uint4 kw4[4];  // four chunks of the row in flight (head_dim 16 and 32 have fewer)
 #pragma unroll
-      for (int gq = 0; gq < G; ++gq) {
-        const uint4 h4 = *reinterpret_cast<const uint4*>(qhi + gq * hd + 16 * c);
-        const uint4 l4 = *reinterpret_cast<const uint4*>(qlo + gq * hd + 16 * c);
-        ih[gq] = dp4a_ss((int)kw.x, (int)h4.x, ih[gq]);
-        ih[gq] = dp4a_ss((int)kw.y, (int)h4.y, ih[gq]);
-        ih[gq] = dp4a_ss((int)kw.z, (int)h4.z, ih[gq]);
-        ih[gq] = dp4a_ss((int)kw.w, (int)h4.w, ih[gq]);
-        il[gq] = dp4a_ss((int)kw.x, (int)l4.x, il[gq]);
-        il[gq] = dp4a_ss((int)kw.y, (int)l4.y, il[gq]);
-        il[gq] = dp4a_ss((int)kw.z, (int)l4.z, il[gq]);
-        il[gq] = dp4a_ss((int)kw.w, (int)l4.w, il[gq]);
+      for (int j = 0; j < 4; ++j)
+        kw4[j] = c0 + j < nchunk ? __ldg(krow + c0 + j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (c0 + j >= nchunk) break;
+        const uint4 kw = kw4[j];
+        const uint32_t c = c0 + j;
+#pragma unroll
+        for (int gq = 0; gq < G; ++gq) {
+          const uint4 h4 = *reinterpret_cast<const uint4*>(qhi + gq * hd + 16 * c);
+          const uint4 l4 = *reinterpret_cast<const uint4*>(qlo + gq * hd + 16 * c);
+          ih[gq] = dp4a_ss((int)kw.x, (int)h4.x, ih[gq]);
+          ih[gq] = dp4a_ss((int)kw.y, (int)h4.y, ih[gq]);
+          ih[gq] = dp4a_ss((int)kw.z, (int)h4.z, ih[gq]);
+          ih[gq] = dp4a_ss((int)kw.w, (int)h4.w, ih[gq]);
+          il[gq] = dp4a_ss((int)kw.x, (int)l4.x, il[gq]);
+          il[gq] = dp4a_ss((int)kw.y, (int)l4.y, il[gq]);
+          il[gq] = dp4a_ss((int)kw.z, (int)l4.z, il[gq]);
+          il[gq] = dp4a_ss((int)kw.w, (int)l4.w, il[gq]);
+        }
       }
     }
 #pragma unroll
@@ -145,9 +190,7 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) psum[gq] = 0.f;
   for (uint32_t i = tid; i < n; i += PA_THREADS) {
-    const uint32_t t = t0 + i;
-    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-    const float vsc = reinterpret_cast<const float*>(rec + a.g.vs_off())[t % bs];
+    const float vsc = vscs[i];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) {
       float e = expf(prob[gq * a.part_tokens + i] - pmax[gq]);
@@ -159,36 +202,46 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   for (int gq = 0; gq < G; ++gq) psum[gq] = block_sum(psum[gq], s_red);
   __syncthreads();
 
-  // --- PV: thread = (dim word c, token slice)
-  const uint32_t words = hd / 4;              // 4 dims per 32-bit word
-  const uint32_t nslice = PA_THREADS / words; // hd in {16..256} -> words in {4..64}
-  const uint32_t c = tid % words, slice = tid / words;
-  float acc[G][4];
+  // --- PV
+  float acc[G][8];
 #pragma unroll
-  for (int gq = 0; gq < G; ++gq) acc[gq][0] = acc[gq][1] = acc[gq][2] = acc[gq][3] = 0.f;
-  for (uint32_t i = slice; i < n; i += nslice) {
-    const uint32_t t = t0 + i;
-    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-    const uint32_t vw = __ldg(reinterpret_cast<const uint32_t*>(rec + a.g.v_off() +
-                                                               (size_t)(t % bs) * hd) + c) ^
-                        0x80808080u;
-    const float f0 = s8_to_f32(vw, 0), f1 = s8_to_f32(vw, 1), f2 = s8_to_f32(vw, 2),
-                f3 = s8_to_f32(vw, 3);
+  for (int gq = 0; gq < G; ++gq)
 #pragma unroll
-    for (int gq = 0; gq < G; ++gq) {
-      const float p = prob[gq * a.part_tokens + i];
-      acc[gq][0] = fmaf(p, f0, acc[gq][0]);
-      acc[gq][1] = fmaf(p, f1, acc[gq][1]);
-      acc[gq][2] = fmaf(p, f2, acc[gq][2]);
-      acc[gq][3] = fmaf(p, f3, acc[gq][3]);
+    for (int k = 0; k < 8; ++k) acc[gq][k] = 0.f;
+  for (uint32_t i0 = slice; i0 < n; i0 += 4 * nslice) {
+    uint2 vnext[4];
+    load_v(i0 + 4 * nslice, vnext);  // nothing is loaded past the partition's end
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t i = i0 + j * nslice;
+      if (i < n) {
+        const uint32_t lo = vcur[j].x ^ 0x80808080u, hi = vcur[j].y ^ 0x80808080u;
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          f[k] = s8_to_f32(lo, k);
+          f[4 + k] = s8_to_f32(hi, k);
+        }
+#pragma unroll
+        for (int gq = 0; gq < G; ++gq) {
+          const float p = prob[gq * a.part_tokens + i];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[gq][k] = fmaf(p, f[k], acc[gq][k]);
+        }
+      }
     }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) vcur[j] = vnext[j];
   }
   // reduce over token slices through shared memory: red[slice][G][hd]
   float4* red4 = reinterpret_cast<float4*>(red);
 #pragma unroll
-  for (int gq = 0; gq < G; ++gq)
-    red4[(slice * G + gq) * words + c] =
+  for (int gq = 0; gq < G; ++gq) {
+    red4[((slice * G + gq) * dwords + c) * 2] =
         make_float4(acc[gq][0], acc[gq][1], acc[gq][2], acc[gq][3]);
+    red4[((slice * G + gq) * dwords + c) * 2 + 1] =
+        make_float4(acc[gq][4], acc[gq][5], acc[gq][6], acc[gq][7]);
+  }
   __syncthreads();
   for (uint32_t e = tid; e < G * hd; e += PA_THREADS) {
     float s = 0.f;
@@ -208,6 +261,55 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
       }
     a.part_ml[(head * a.num_parts + part) * 2 + 0] = m;
     a.part_ml[(head * a.num_parts + part) * 2 + 1] = l;
+  }
+  if (!a.tickets) return;  // a separate stage-2 launch merges
+
+  // --- merge, by the CTA that draws the last ticket of this (sequence, kv head)
+  __shared__ uint32_t s_last;
+  // partitions that exist in this grid (a context longer than the host said is cut off there)
+  const uint32_t np = min((ctx + a.part_tokens - 1) / a.part_tokens, a.num_parts);
+  __threadfence();  // this CTA's partials are visible device-wide before its ticket is
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* ticket = a.tickets + (size_t)seq * a.g.kv_heads + kvh;
+    const uint32_t drawn = atomicAdd(ticket, 1u);
+    s_last = drawn == np - 1;
+    if (s_last) *ticket = 0;  // every CTA of the group has drawn: ready for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // weights e^{m_p - M} per (head, partition) into shared memory (the probabilities are dead)
+  float* wts = prob;               // [G][np], np <= part_tokens (checked by the host)
+  float* invs = vscs;              // [G]
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int gq = warp; gq < G; gq += PA_THREADS / 32) {
+      const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
+      const float* ml = a.part_ml + head * a.num_parts * 2;
+      float M = -INFINITY;
+      for (uint32_t p = lane; p < np; p += 32) M = fmaxf(M, __ldcg(ml + 2 * p));
+#pragma unroll
+      for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+      float denom = 0.f;
+      for (uint32_t p = lane; p < np; p += 32) {
+        const float w = expf(__ldcg(ml + 2 * p) - M);
+        wts[gq * np + p] = w;
+        denom += __ldcg(ml + 2 * p + 1) * w;
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xFFFFFFFFu, denom, o);
+      if (lane == 0) invs[gq] = denom > 0.f ? 1.0f / denom : 0.f;
+    }
+  }
+  __syncthreads();
+  for (uint32_t e = tid; e < G * hd; e += PA_THREADS) {
+    const uint32_t gq = e / hd, d = e % hd;
+    const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
+    const float* pa = a.part_acc + head * a.num_parts * hd + d;
+    float s = 0.f;
+    for (uint32_t p = 0; p < np; ++p) s += __ldcg(pa + (size_t)p * hd) * wts[gq * np + p];
+    a.out[head * hd + d] = s * invs[gq];
   }
 }
 
@@ -268,6 +370,18 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
   return KANSO_OK;
 }
 
+// Dynamic shared memory of stage 1: query planes and scales, block ids, probabilities,
+// V scales, PV reduction scratch.
+static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t block_size) {
+  const uint32_t nblk_part = ((pt + block_size - 1) / block_size + 4) & ~3u;
+  const uint32_t dwords = hd / 8, nslice = PA_THREADS / dwords;
+  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4 +
+                (size_t)((pt + 3) & ~3u) * 4;
+  size_t red_bytes = (size_t)nslice * G * hd * 4;
+  if (red_bytes < 128) red_bytes = 128;
+  return smem + red_bytes;
+}
+
 template <int G>
 static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
   static size_t smem_set[16] = {0};
@@ -320,13 +434,13 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   a.num_parts = nparts;
   a.scale = p->scale;
   a.status = ctx->dev_status;
+  // merge inside stage 1 when the ticket array covers the batch and the partition weights fit
+  // where the probabilities were
+  const bool merge_in_stage1 =
+      (uint64_t)p->num_seqs * p->num_kv_heads <= kanso_cuda_ctx::kPaTickets && nparts <= pt;
+  a.tickets = merge_in_stage1 ? ctx->pa_tickets : nullptr;
 
-  const uint32_t nblk_part = ((pt + p->block_size - 1) / p->block_size + 4) & ~3u;
-  const uint32_t words = hd / 4, nslice = PA_THREADS / words;
-  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4;
-  size_t red_bytes = (size_t)nslice * G * hd * 4;
-  if (red_bytes < 128) red_bytes = 128;
-  smem += red_bytes;
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: %zu bytes of shared memory needed",
                 smem);
@@ -342,7 +456,7 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
     default: launch_stage1<8>(ctx, a, grid, smem); break;
   }
   int32_t st = after_launch(ctx, "paged_attention stage 1");
-  if (st) return st;
+  if (st || merge_in_stage1) return st;
   launch_dependent(ctx, paged_attn_stage2, dim3(p->num_heads, p->num_seqs), dim3(64), 0, a);
   return after_launch(ctx, "paged_attention stage 2");
 }
@@ -493,13 +607,9 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.num_parts = nparts;
   a.scale = p->scale;
   a.status = ctx->dev_status;
+  a.tickets = nullptr;  // two launches: stage 2 merges
 
-  const uint32_t nblk_part = ((pt + p->block_size - 1) / p->block_size + 4) & ~3u;
-  const uint32_t words = hd / 4, nslice = PA_THREADS / words;
-  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4;
-  size_t red_bytes = (size_t)nslice * G * hd * 4;
-  if (red_bytes < 128) red_bytes = 128;
-  smem += red_bytes;
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "paged_attention_noalloc: %zu bytes of shared memory needed", smem);
