@@ -79,7 +79,7 @@ struct Q8mRaw {
 
 // NBT = blocks per warp slice, PD = row groups whose weights are in flight per warp = row
 // groups between two reductions.
-template <int MODE>
+template <int MODE, bool COOP>
 __global__ void __launch_bounds__(Q8M_THREADS, 2) gemv_q8_mma_kernel(const Q8mArgs a) {
   constexpr int NBT = Q8M_NB;
   constexpr int PLANES = MODE == Q8M_MODE_C ? 1 : 2;
@@ -133,119 +133,258 @@ __global__ void __launch_bounds__(Q8M_THREADS, 2) gemv_q8_mma_kernel(const Q8mAr
 #pragma unroll
   for (int p = 0; p < PD; ++p)
     if (g_begin + p < g_end) load_group(g_begin + p, raw[p]);
-  pdl_launch_dependents();
-  pdl_wait();
-
-  // ---- activation fragments of this warp's K slice
   // B column g of the MMA: activation row mcol (and plane, in mode A)
   const int mcol = MODE == Q8M_MODE_A ? g >> 1 : g;
   const int plane = MODE == Q8M_MODE_A ? g & 1 : 0;
-  uint32_t bh[NBT][2];  // plane used by the first (or only) MMA
+  constexpr int MROWS = MODE == Q8M_MODE_A ? 4 : 8;  // activation rows a launch may carry
+  uint32_t bh[NBT][2];  // activation fragments: plane used by the first (or only) MMA
   uint32_t bl[MODE == Q8M_MODE_B ? NBT : 1][2];
   float dx[NBT][NCOL];  // activation scale per block for this lane's C columns
-  float ss = 0.f;       // sum of squares of row mcol over this warp's slice
+  // Few activation rows (COOP): the warp's lanes share the quantisation of every (row, block)
+  // pair. More rows: each lane quantises the k-words of its own MMA column.
+  float nwv[NBT];
+  if (COOP) {
+
+    // The norm weights are weights: read before the wait. Lane = element of the block.
 #pragma unroll
-  for (int j = 0; j < NBT; ++j) {
-    float v[2][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[h][e] = 0.f;
-    const int kb = kb0 + j;
-    if (j < nb && mcol < a.M) {
-      // k-words t and 4 + t of the block, in the order the weights feed the MMA
-      const float* xb = a.x + (int64_t)mcol * a.ldx + 32 * kb;
-      const float* x2b = a.x2 ? a.x2 + (int64_t)mcol * a.ldx + 32 * kb : nullptr;
-      const float* nwb = a.norm_w ? a.norm_w + 32 * kb : nullptr;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int kw = 4 * h + t;
-        int k0, k1;  // first element of the two halves of the k-word
-        if (kb & 1) {
-          k0 = 4 * kw;
-          k1 = 4 * kw + 2;
-        } else {
-          k0 = (4 * kw + 2) & 31;
-          k1 = (4 * kw + 4) & 31;
-        }
-        const float2 p0 = *reinterpret_cast<const float2*>(xb + k0);
-        const float2 p1 = *reinterpret_cast<const float2*>(xb + k1);
-        v[h][0] = p0.x; v[h][1] = p0.y; v[h][2] = p1.x; v[h][3] = p1.y;
-        if (x2b) {  // silu(g) * u with silu(g) = g / (1 + e^-g)
-          const float2 u0 = *reinterpret_cast<const float2*>(x2b + k0);
-          const float2 u1 = *reinterpret_cast<const float2*>(x2b + k1);
-          v[h][0] = v[h][0] / (1.0f + expf(-v[h][0])) * u0.x;
-          v[h][1] = v[h][1] / (1.0f + expf(-v[h][1])) * u0.y;
-          v[h][2] = v[h][2] / (1.0f + expf(-v[h][2])) * u1.x;
-          v[h][3] = v[h][3] / (1.0f + expf(-v[h][3])) * u1.y;
-        }
-        if (nwb) {
-          const float2 n0 = __ldg(reinterpret_cast<const float2*>(nwb + k0));
-          const float2 n1 = __ldg(reinterpret_cast<const float2*>(nwb + k1));
-#pragma unroll
-          for (int e = 0; e < 4; ++e) ss = fmaf(v[h][e], v[h][e], ss);
-          v[h][0] *= n0.x; v[h][1] *= n0.y; v[h][2] *= n1.x; v[h][3] *= n1.y;
-        }
-      }
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[h][e]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    float d, id;
-    if (PLANES == 1) {  // exactly quantize_row_q8_0
-      d = __fdiv_rn(amax, 127.0f);
-      id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    } else {  // the second plane absorbs the last-bit differences of the fast forms
-      d = amax * (1.0f / 127.0f);
-      id = d != 0.0f ? __frcp_rn(d) : 0.0f;
-    }
-    float hq[2][4], lq[2][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float scaled = __fmul_rn(v[h][e], id);
-        hq[h][e] = fminf(fmaxf(PLANES == 1 ? roundf(scaled) : rintf(scaled), -128.f), 127.f);
-        if (PLANES == 2)
-          lq[h][e] =
-              fminf(fmaxf(rintf(fmaf(-d, hq[h][e], v[h][e]) * (254.0f * id)), -127.f), 127.f);
-      }
-    if (MODE == Q8M_MODE_A) {
-      bh[j][0] = plane ? q8m_pack4(lq[0]) : q8m_pack4(hq[0]);
-      bh[j][1] = plane ? q8m_pack4(lq[1]) : q8m_pack4(hq[1]);
-    } else {
-      bh[j][0] = q8m_pack4(hq[0]);
-      bh[j][1] = q8m_pack4(hq[1]);
-      if (MODE == Q8M_MODE_B) {
-        bl[j][0] = q8m_pack4(lq[0]);
-        bl[j][1] = q8m_pack4(lq[1]);
-      }
-    }
-    // scales of the activation rows this lane's C columns belong to
-    const float dsc = PLANES == 2 ? d * (1.0f / 254.0f) : d;
-    dx[j][0] = __shfl_sync(0xFFFFFFFFu, dsc, 8 * t);  // column 2t (mode A: row t, plane 0)
-    if (NCOL == 2) dx[j][NCOL - 1] = __shfl_sync(0xFFFFFFFFu, dsc, 8 * t + 4);  // column 2t + 1
+    for (int j = 0; j < NBT; ++j)
+      nwv[j] = (a.norm_w && j < nb) ? __ldg(a.norm_w + 32 * (kb0 + j) + lane) : 1.0f;
   }
-  if (a.norm_w) {
-    // 1 / rms of every activation row: this warp's slice, then all warps (the host does not
-    // split K across CTAs when a norm is folded in, so the CTA sees the whole row)
-    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
-    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
-    if (t == 0 && plane == 0) s_ss[warp][mcol] = ss;
-    __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait();
+  if (COOP) {
+
+    // ---- activation fragments of this warp's K slice. The 32 lanes quantise the 32 values of
+    // one (activation row, block) pair together, one value each; the bytes are then gathered
+    // into 32-bit words inside each quad of lanes and handed to the lanes that own the matching
+    // MMA column with shuffles. Every load is issued before any arithmetic.
+    float xv[MROWS][NBT], uv[MROWS][NBT];
 #pragma unroll
-    for (int cidx = 0; cidx < NCOL; ++cidx) {
-      const int m = MODE == Q8M_MODE_A ? t : 2 * t + cidx;
-      float tot = 0.f;
-      if (m < a.M)
-        for (int w = 0; w < Q8M_WARPS; ++w) tot += s_ss[w][m];
-      const float r = 1.0f / sqrtf(tot / (float)a.K + a.eps);
+    for (int m = 0; m < MROWS; ++m)
 #pragma unroll
-      for (int j = 0; j < NBT; ++j) dx[j][cidx] *= r;
+      for (int j = 0; j < NBT; ++j) {
+        xv[m][j] = 0.f;
+        uv[m][j] = 1.f;
+        if (m < a.M && j < nb) {
+          const int64_t at = (int64_t)m * a.ldx + 32 * (kb0 + j) + lane;
+          xv[m][j] = a.x[at];
+          if (a.x2) uv[m][j] = a.x2[at];
+        }
+      }
+#pragma unroll
+    for (int j = 0; j < NBT; ++j) {
+      bh[j][0] = bh[j][1] = 0u;
+      if (MODE == Q8M_MODE_B) bl[j][0] = bl[j][1] = 0u;
+#pragma unroll
+      for (int cidx = 0; cidx < NCOL; ++cidx) dx[j][cidx] = 0.f;
+    }
+    float ss[MROWS];  // per activation row: this lane's share of the sum of squares
+#pragma unroll
+    for (int m = 0; m < MROWS; ++m) {
+      ss[m] = 0.f;
+      if (m < a.M) {
+#pragma unroll
+        for (int j = 0; j < NBT; ++j) {
+          float x = xv[m][j];
+          if (a.x2) x = x / (1.0f + expf(-x)) * uv[m][j];  // silu(g) * u
+          if (a.norm_w) {
+            ss[m] = fmaf(x, x, ss[m]);
+            x *= nwv[j];
+          }
+          float amax = fabsf(x);
+#pragma unroll
+          for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+          float d, id;
+          if (PLANES == 1) {  // exactly quantize_row_q8_0
+            d = __fdiv_rn(amax, 127.0f);
+            id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+          } else {  // the second plane absorbs the last-bit differences of the fast forms
+            d = amax * (1.0f / 127.0f);
+            id = d != 0.0f ? __frcp_rn(d) : 0.0f;
+          }
+          const float scaled = __fmul_rn(x, id);
+          const float hq = fminf(fmaxf(PLANES == 1 ? roundf(scaled) : rintf(scaled), -128.f), 127.f);
+          float lq = 0.f;
+          if (PLANES == 2)
+            lq = fminf(fmaxf(rintf(fmaf(-d, hq, x) * (254.0f * id)), -127.f), 127.f);
+          // words of four consecutive elements, complete in every lane of the quad
+          const int sh8 = 8 * (lane & 3);
+          uint32_t hw = ((uint32_t)(int)hq & 0xFFu) << sh8, lw = ((uint32_t)(int)lq & 0xFFu) << sh8;
+          hw |= __shfl_xor_sync(0xFFFFFFFFu, hw, 1);
+          hw |= __shfl_xor_sync(0xFFFFFFFFu, hw, 2);
+          if (PLANES == 2) {
+            lw |= __shfl_xor_sync(0xFFFFFFFFu, lw, 1);
+            lw |= __shfl_xor_sync(0xFFFFFFFFu, lw, 2);
+          }
+          // k-word kw of the block in the order its weights feed the MMA: the natural word, or
+          // (block starting on a word) the bytes 4kw+2 .. 4kw+5, wrapping at 32
+          const bool rotated = ((kb0 + j) & 1) == 0;
+          auto kword = [&](uint32_t w, int kw) {
+            const uint32_t lo = __shfl_sync(0xFFFFFFFFu, w, 4 * kw);
+            const uint32_t hi = __shfl_sync(0xFFFFFFFFu, w, 4 * ((kw + 1) & 7));
+            return rotated ? __funnelshift_r(lo, hi, 16) : lo;
+          };
+          const float dsc = PLANES == 2 ? d * (1.0f / 254.0f) : d;
+          if (MODE == Q8M_MODE_A) {
+            // odd lanes of a quad offer the low plane, even lanes the high plane
+            const uint32_t offer = (lane & 1) ? lw : hw;
+            const uint32_t lo0 = __shfl_sync(0xFFFFFFFFu, offer, 4 * t + plane);
+            const uint32_t hi0 = __shfl_sync(0xFFFFFFFFu, offer, 4 * ((t + 1) & 7) + plane);
+            const uint32_t lo1 = __shfl_sync(0xFFFFFFFFu, offer, 4 * (4 + t) + plane);
+            const uint32_t hi1 = __shfl_sync(0xFFFFFFFFu, offer, 4 * ((5 + t) & 7) + plane);
+            if (mcol == m) {
+              bh[j][0] = rotated ? __funnelshift_r(lo0, hi0, 16) : lo0;
+              bh[j][1] = rotated ? __funnelshift_r(lo1, hi1, 16) : lo1;
+            }
+            if (t == m) dx[j][0] = dsc;
+          } else {
+            const uint32_t h0 = kword(hw, t), h1 = kword(hw, 4 + t);
+            if (mcol == m) {
+              bh[j][0] = h0;
+              bh[j][1] = h1;
+            }
+            if (MODE == Q8M_MODE_B) {
+              const uint32_t l0 = kword(lw, t), l1 = kword(lw, 4 + t);
+              if (mcol == m) {
+                bl[j][0] = l0;
+                bl[j][1] = l1;
+              }
+            }
+            if (2 * t == m) dx[j][0] = dsc;
+            if (2 * t + 1 == m) dx[j][NCOL - 1] = dsc;
+          }
+        }
+      }
+    }
+    if (a.norm_w) {
+      // 1 / rms of every activation row: this warp's slice, then all warps (the host does not
+      // split K across CTAs when a norm is folded in, so the CTA sees the whole row)
+#pragma unroll
+      for (int m = 0; m < MROWS; ++m) {
+        if (m < a.M) {
+          float v = ss[m];
+#pragma unroll
+          for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+          if (lane == 0) s_ss[warp][m] = v;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int cidx = 0; cidx < NCOL; ++cidx) {
+        const int m = MODE == Q8M_MODE_A ? t : 2 * t + cidx;
+        float tot = 0.f;
+        if (m < a.M)
+          for (int w = 0; w < Q8M_WARPS; ++w) tot += s_ss[w][m];
+        const float r = 1.0f / sqrtf(tot / (float)a.K + a.eps);
+#pragma unroll
+        for (int j = 0; j < NBT; ++j) dx[j][cidx] *= r;
+      }
+    }
+  } else {
+    float ss = 0.f;  // sum of squares of row mcol over this warp's slice
+#pragma unroll
+    for (int j = 0; j < NBT; ++j) {
+      float v[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[h][e] = 0.f;
+      const int kb = kb0 + j;
+      if (j < nb && mcol < a.M) {
+        // k-words t and 4 + t of the block, in the order the weights feed the MMA
+        const float* xb = a.x + (int64_t)mcol * a.ldx + 32 * kb;
+        const float* x2b = a.x2 ? a.x2 + (int64_t)mcol * a.ldx + 32 * kb : nullptr;
+        const float* nwb = a.norm_w ? a.norm_w + 32 * kb : nullptr;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int kw = 4 * h + t;
+          int k0, k1;  // first element of the two halves of the k-word
+          if (kb & 1) {
+            k0 = 4 * kw;
+            k1 = 4 * kw + 2;
+          } else {
+            k0 = (4 * kw + 2) & 31;
+            k1 = (4 * kw + 4) & 31;
+          }
+          const float2 p0 = *reinterpret_cast<const float2*>(xb + k0);
+          const float2 p1 = *reinterpret_cast<const float2*>(xb + k1);
+          v[h][0] = p0.x; v[h][1] = p0.y; v[h][2] = p1.x; v[h][3] = p1.y;
+          if (x2b) {  // silu(g) * u with silu(g) = g / (1 + e^-g)
+            const float2 u0 = *reinterpret_cast<const float2*>(x2b + k0);
+            const float2 u1 = *reinterpret_cast<const float2*>(x2b + k1);
+            v[h][0] = v[h][0] / (1.0f + expf(-v[h][0])) * u0.x;
+            v[h][1] = v[h][1] / (1.0f + expf(-v[h][1])) * u0.y;
+            v[h][2] = v[h][2] / (1.0f + expf(-v[h][2])) * u1.x;
+            v[h][3] = v[h][3] / (1.0f + expf(-v[h][3])) * u1.y;
+          }
+          if (nwb) {
+            const float2 n0 = __ldg(reinterpret_cast<const float2*>(nwb + k0));
+            const float2 n1 = __ldg(reinterpret_cast<const float2*>(nwb + k1));
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(v[h][e], v[h][e], ss);
+            v[h][0] *= n0.x; v[h][1] *= n0.y; v[h][2] *= n1.x; v[h][3] *= n1.y;
+          }
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[h][e]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+      float d, id;
+      if (PLANES == 1) {  // exactly quantize_row_q8_0
+        d = __fdiv_rn(amax, 127.0f);
+        id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+      } else {  // the second plane absorbs the last-bit differences of the fast forms
+        d = amax * (1.0f / 127.0f);
+        id = d != 0.0f ? __frcp_rn(d) : 0.0f;
+      }
+      float hq[2][4], lq[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float scaled = __fmul_rn(v[h][e], id);
+          hq[h][e] = fminf(fmaxf(PLANES == 1 ? roundf(scaled) : rintf(scaled), -128.f), 127.f);
+          if (PLANES == 2)
+            lq[h][e] =
+                fminf(fmaxf(rintf(fmaf(-d, hq[h][e], v[h][e]) * (254.0f * id)), -127.f), 127.f);
+        }
+      if (MODE == Q8M_MODE_A) {
+        bh[j][0] = plane ? q8m_pack4(lq[0]) : q8m_pack4(hq[0]);
+        bh[j][1] = plane ? q8m_pack4(lq[1]) : q8m_pack4(hq[1]);
+      } else {
+        bh[j][0] = q8m_pack4(hq[0]);
+        bh[j][1] = q8m_pack4(hq[1]);
+        if (MODE == Q8M_MODE_B) {
+          bl[j][0] = q8m_pack4(lq[0]);
+          bl[j][1] = q8m_pack4(lq[1]);
+        }
+      }
+      // scales of the activation rows this lane's C columns belong to
+      const float dsc = PLANES == 2 ? d * (1.0f / 254.0f) : d;
+      dx[j][0] = __shfl_sync(0xFFFFFFFFu, dsc, 8 * t);  // column 2t (mode A: row t, plane 0)
+      if (NCOL == 2) dx[j][NCOL - 1] = __shfl_sync(0xFFFFFFFFu, dsc, 8 * t + 4);  // column 2t + 1
+    }
+    if (a.norm_w) {
+      // 1 / rms of every activation row: this warp's slice, then all warps (the host does not
+      // split K across CTAs when a norm is folded in, so the CTA sees the whole row)
+      ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
+      ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
+      if (t == 0 && plane == 0) s_ss[warp][mcol] = ss;
+      __syncthreads();
+#pragma unroll
+      for (int cidx = 0; cidx < NCOL; ++cidx) {
+        const int m = MODE == Q8M_MODE_A ? t : 2 * t + cidx;
+        float tot = 0.f;
+        if (m < a.M)
+          for (int w = 0; w < Q8M_WARPS; ++w) tot += s_ss[w][m];
+        const float r = 1.0f / sqrtf(tot / (float)a.K + a.eps);
+#pragma unroll
+        for (int j = 0; j < NBT; ++j) dx[j][cidx] *= r;
+      }
     }
   }
 
@@ -344,8 +483,11 @@ __global__ void __launch_bounds__(Q8M_THREADS, 2) gemv_q8_mma_kernel(const Q8mAr
 
 template <int MODE>
 static int32_t q8m_launch(kanso_cuda_ctx* ctx, const Q8mArgs& a, dim3 grid) {
-  cudaError_t e =
-      launch_dependent(ctx, gemv_q8_mma_kernel<MODE>, grid, dim3(Q8M_THREADS), 0, a);
+  // up to two activation rows: the lanes quantise each (row, block) pair together
+  cudaError_t e = a.M <= 2 ? launch_dependent(ctx, gemv_q8_mma_kernel<MODE, true>, grid,
+                                              dim3(Q8M_THREADS), 0, a)
+                           : launch_dependent(ctx, gemv_q8_mma_kernel<MODE, false>, grid,
+                                              dim3(Q8M_THREADS), 0, a);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_q8_mma launch");
   return after_launch(ctx, "gemv_q8_mma");
 }
@@ -357,7 +499,7 @@ static int32_t q8m_launch(kanso_cuda_ctx* ctx, const Q8mArgs& a, dim3 grid) {
 int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
                       const int64_t* rows, const float* x, const float* x2, const float* norm_w,
                       float eps, const float* resid, int64_t K, int M, int32_t act_mode,
-                      bool* handled) {
+                      bool decode_chain, bool* handled) {
   *handled = false;
   if (nseg < 1 || nseg > Q8M_MAX_SEGS || M < 1 || M > 8) return KANSO_OK;
   if (K < 64 || K % 64 != 0 || K > (1 << 20)) return KANSO_OK;
@@ -368,13 +510,15 @@ int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float
   const int ksplit = (bpr + Q8M_NB * Q8M_WARPS - 1) / (Q8M_NB * Q8M_WARPS);
   if (ksplit > 1 && (norm_w || nseg != 1)) return KANSO_OK;
   if (ksplit > 65535) return KANSO_OK;
-  // One activation row: the streaming kernel (bulk copies into shared memory, dp4a) is faster
-  // except on tall matrices with short rows (an LM head), where this kernel's two row groups
-  // in flight per warp win. From two rows on, this kernel's cost no longer grows with M.
+  // One activation row, called on its own: the streaming kernel (bulk copies into shared
+  // memory, dp4a) sustains more launches per second, except on tall matrices with short rows
+  // (an LM head). Inside the decode step's chain of dependent launches this kernel is used for
+  // every row count: what counts there is the time from the arrival of the activations to the
+  // last store, and this kernel has no block-wide activation staging in that path.
   {
     int64_t total_rows = 0;
     for (int i = 0; i < nseg; ++i) total_rows += rows[i];
-    if (M == 1 && !(ksplit == 1 && total_rows >= 16384)) return KANSO_OK;
+    if (M == 1 && !decode_chain && !(ksplit == 1 && total_rows >= 16384)) return KANSO_OK;
   }
   Q8mArgs a;
   a.nseg = nseg;

@@ -535,7 +535,10 @@ static int32_t launch_stream(kanso_cuda_ctx* ctx, const StreamCall& c) {
     if (tr > share) tr = (int)share;
     if (tr < R) tr = R;
     int sb = ((tr * a.row_bytes + 15) & ~15) + 32;
-    for (int st = MAX_STAGES; st >= 2; --st) {
+    // no more stages than this warp has tiles: a small launch then leaves shared memory for
+    // the CTAs of the launches after it, which prefetch their weights while this one runs
+    const int tiles = (int)((share + tr - 1) / tr);
+    for (int st = tiles < MAX_STAGES ? (tiles < 1 ? 1 : tiles) : MAX_STAGES; st >= 1; --st) {
       StreamLayout L = stream_layout<FMT, PLANES>(a.K, a.bpr, c.M, nw, st, sb);
       if (L.total <= smem_max) {
         best_w = nw;
@@ -611,7 +614,7 @@ static int32_t dispatch_m(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
 int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
                       const int64_t* rows, const float* x, const float* x2, const float* norm_w,
                       float eps, const float* resid, int64_t K, int M, int32_t act_mode,
-                      bool* handled);
+                      bool decode_chain, bool* handled);
 
 int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
                           const int64_t* rows, const float* x, const float* x2,
@@ -626,7 +629,7 @@ int32_t stream_fused_q8_0(kanso_cuda_ctx* ctx, int nseg, const void* const* w, f
     // the tensor-core kernel takes the shapes it covers (K a multiple of 64, at most 4096)
     bool handled = false;
     int32_t st = q8_mma_matmul(ctx, nseg, w, y, rows, x, x2, norm_w, eps, resid, K, M, act_mode,
-                               &handled);
+                               true, &handled);
     if (st != KANSO_OK || handled) return st;
   }
   StreamCall c;

@@ -56,94 +56,6 @@ __global__ void rope_kernel(float* __restrict__ x, const uint32_t* __restrict__ 
   }
 }
 
-// Decode-step glue in one launch (src/model.rs:1164-1171): rotate-half RoPE of the query
-// heads in place, RoPE of the key heads, and the int8 quantising write of the roped K and of
-// V into the pool (quantize_head_slice, src/kv_cache/quantized_storage.rs:452-469).
-// One warp per (token, slot): slots [0, H) = query heads, [H, H+KH) = key heads, the rest = V.
-// Multiplies and adds round separately, as the reference's tensor ops do, so the stored
-// bytes equal the CPU path's.
-__global__ void rope_kv_write_kernel(float* __restrict__ q, const float* __restrict__ k,
-                                     const float* __restrict__ v,
-                                     const uint32_t* __restrict__ positions,
-                                     const uint32_t* __restrict__ slots, int64_t T, int H,
-                                     const float* __restrict__ cos_t,
-                                     const float* __restrict__ sin_t, int table_len, KvGeom g,
-                                     uint32_t layer, int* status) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int KH = (int)g.kv_heads, hd = (int)g.head_dim, half = hd / 2;
-  const int nslot = H + 2 * KH;
-  if (wid >= T * nslot) return;
-  const int64_t t = wid / nslot;
-  const int slot = (int)(wid - t * nslot);
-  const uint32_t pos = positions[t];
-  if (pos >= (uint32_t)table_len) {
-    if (lane == 0) atomicOr(status, DEV_BAD_INDEX);
-    return;
-  }
-  constexpr int MAXP = 4;  // head_dim <= 256: at most 4 (first, second) pairs per lane
-  float a[MAXP], b[MAXP];
-  const bool is_q = slot < H, is_k = !is_q && slot < H + KH;
-  const int head = is_q ? slot : (is_k ? slot - H : slot - H - KH);
-  const float* src = is_q ? q + (t * H + head) * hd
-                          : (is_k ? k : v) + (t * KH + head) * hd;
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int j = lane + 32 * i;
-    a[i] = b[i] = 0.f;
-    if (j < half) {
-      float x0 = src[j], x1 = src[j + half];
-      if (is_q || is_k) {
-        const float c = cos_t[(int64_t)pos * half + j], s = sin_t[(int64_t)pos * half + j];
-        const float r0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        const float r1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-        x0 = r0;
-        x1 = r1;
-      }
-      a[i] = x0;
-      b[i] = x1;
-      amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
-    }
-  }
-  if (is_q) {
-    float* dst = q + (t * H + head) * hd;
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const int j = lane + 32 * i;
-      if (j < half) {
-        dst[j] = a[i];
-        dst[j + half] = b[i];
-      }
-    }
-    return;
-  }
-  const uint32_t sl = slots[t];
-  const uint32_t block = sl / g.block_size, off = sl % g.block_size;
-  if (block >= g.num_blocks) {
-    if (lane == 0) atomicOr(status, DEV_BAD_INDEX);
-    return;
-  }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-  const float inv = __fdiv_rn(1.0f, scale);
-  uint8_t* rec = g.pool + g.rec_offset(layer, block, head);
-  int8_t* dst =
-      reinterpret_cast<int8_t*>(rec + (is_k ? g.k_off() : g.v_off())) + (size_t)off * hd;
-#pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int j = lane + 32 * i;
-    if (j < half) {
-      dst[j] = (int8_t)fminf(fmaxf(roundf(__fmul_rn(a[i], inv)), -127.f), 127.f);
-      dst[j + half] = (int8_t)fminf(fmaxf(roundf(__fmul_rn(b[i], inv)), -127.f), 127.f);
-    }
-  }
-  if (lane == 0) reinterpret_cast<float*>(rec + (is_k ? g.ks_off() : g.vs_off()))[off] = scale;
-}
-
 __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                 float* __restrict__ out, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -219,19 +131,6 @@ int32_t launch_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, in
   rope_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(x, positions, (int)heads, (int)head_dim, freq,
                                                     cos_t, sin_t, table_len, ctx->dev_status);
   return after_launch(ctx, "rope");
-}
-
-int32_t launch_rope_kv_write(kanso_cuda_ctx* ctx, float* q, const float* k, const float* v,
-                             const uint32_t* positions, const uint32_t* slots, int64_t T, int H,
-                             const float* cos_t, const float* sin_t, int table_len,
-                             const KvGeom& g, uint32_t layer) {
-  const int64_t warps = T * (H + 2 * (int64_t)g.kv_heads);
-  cudaError_t e = launch_dependent(ctx, rope_kv_write_kernel,
-                                   dim3((unsigned)((warps * 32 + 127) / 128)), dim3(128), 0, q, k,
-                                   v, positions, slots, T, H, cos_t, sin_t, table_len, g, layer,
-                                   ctx->dev_status);
-  if (e != cudaSuccess) return cuda_fail(ctx, e, "rope_kv_write launch");
-  return after_launch(ctx, "rope_kv_write");
 }
 
 int32_t launch_silu_mul(kanso_cuda_ctx* ctx, const float* g, const float* u, float* out,

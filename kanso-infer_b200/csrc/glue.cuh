@@ -37,10 +37,18 @@ int32_t launch_rope(kanso_cuda_ctx* ctx, float* x, const uint32_t* positions, in
                     int64_t heads, int64_t head_dim, float theta, const float* cos_t,
                     const float* sin_t, int table_len);
 struct KvGeom;
-int32_t launch_rope_kv_write(kanso_cuda_ctx* ctx, float* q, const float* k, const float* v,
-                             const uint32_t* positions, const uint32_t* slots, int64_t T, int H,
-                             const float* cos_t, const float* sin_t, int table_len,
-                             const KvGeom& g, uint32_t layer);
+// Inputs of the decode step's attention fusion: un-rotated q goes in as the attention's q; the
+// newest token's K and V, their positions and pool slots, and the RoPE tables.
+struct PaDecodeFusion {
+  const float* k_new;
+  const float* v_new;
+  const uint32_t* positions;
+  const uint32_t* slots;
+  const float* cos_t;
+  const float* sin_t;
+  int table_len;
+};
+
 int32_t launch_silu_mul(kanso_cuda_ctx* ctx, const float* g, const float* u, float* out,
                         int64_t n);
 int32_t launch_residual_add(kanso_cuda_ctx* ctx, float* h, const float* p, int64_t n);

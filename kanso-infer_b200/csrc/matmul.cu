@@ -14,7 +14,7 @@ int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
 int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float* const* y,
                       const int64_t* rows, const float* x, const float* x2, const float* norm_w,
                       float eps, const float* resid, int64_t K, int M, int32_t act_mode,
-                      bool* handled);
+                      bool decode_chain, bool* handled);
 
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
@@ -55,7 +55,7 @@ int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const
       float* y1[1] = {y + m0 * N};
       const int64_t r1[1] = {N};
       int32_t st = q8_mma_matmul(ctx, 1, w1, y1, r1, x + m0 * K, nullptr, nullptr, 0.f, nullptr, K,
-                                 (int)(M - m0 < 8 ? M - m0 : 8), act_mode, &handled);
+                                 (int)(M - m0 < 8 ? M - m0 : 8), act_mode, false, &handled);
       if (st != KANSO_OK) return st;
       if (!handled) all = false;
     }

@@ -11,7 +11,7 @@ namespace kanso {
 int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
                                const float* q, const uint32_t* tables, const uint32_t* lens,
                                float* out, const kanso_paged_attention_params* p,
-                               uint32_t max_ctx_hint);
+                               uint32_t max_ctx_hint, const PaDecodeFusion* fusion);
 
 // Embedding rows of a Q8_0 table (src/weights.rs:50-57), bit-exact d * (f32)q.
 __global__ void model_embed_kernel(const uint8_t* __restrict__ w, const uint32_t* __restrict__ ids,
@@ -281,14 +281,18 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
   if ((st = after_launch(ctx, "embed"))) return st;
   const ModelLin& head = m->output.dev ? m->output : m->token_embd;  // tied lm_head
 
-  // Up to 8 sequences on Q8_0 weights: 7 launches per layer. The norms are folded into the
+  // RoPE of q and of the new k, and the int8 store of the new K/V rows, run inside the
+  // attention kernel. context_lens counts the new token, whose row is slots[seq] and must be
+  // where block_tables places position context_len - 1.
+  const PaDecodeFusion fusion = {k, v, positions, slots, m->rope_cos, m->rope_sin, m->rope_len};
+
+  // Up to 8 sequences on Q8_0 weights: 5 launches per layer. The norms are folded into the
   // activation staging of the projections that follow them, SiLU*up into ffn_down's, the
-  // residual adds into the epilogues, RoPE and the KV write into one kernel.
+  // residual adds into the epilogues, the split-context merge into the attention kernel.
   bool fused = B <= 8 && head.dtype == KANSO_DTYPE_Q8_0;
   for (uint32_t l = 0; l < c.num_hidden_layers && fused; ++l)
     for (const auto& w : m->layers[l].w) fused = fused && w.dev && w.dtype == KANSO_DTYPE_Q8_0;
   if (fused) {
-    const KvGeom g = kv_geom(kv);
     for (uint32_t l = 0; l < c.num_hidden_layers; ++l) {
       auto& ly = m->layers[l];
       if (!ly.attn_norm || !ly.ffn_norm)
@@ -302,11 +306,9 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
                                     c.rms_norm_eps, nullptr, hidden, (int)B, act_mode)))
           return st;
       }
-      if ((st = launch_rope_kv_write(ctx, q, k, v, positions, slots, B, (int)H, m->rope_cos,
-                                     m->rope_sin, m->rope_len, g, l)))
-        return st;
+      // RoPE of q and k and the int8 store of the new K/V rows happen inside the attention
       if ((st = launch_paged_attention(ctx, kv, l, q, block_tables, context_lens, m->attn, &pa,
-                                       max_ctx)))
+                                       max_ctx, &fusion)))
         return st;
       {
         const void* w1[1] = {ly.w[KANSO_W_ATTN_OUTPUT].dev};
@@ -349,11 +351,8 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_Q], m->normed, q, B, act_mode))) return st;
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_K], m->normed, k, B, act_mode))) return st;
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_V], m->normed, v, B, act_mode))) return st;
-    if ((st = launch_rope_kv_write(ctx, q, k, v, positions, slots, B, (int)H, m->rope_cos,
-                                   m->rope_sin, m->rope_len, kv_geom(kv), l)))
-      return st;
     if ((st = launch_paged_attention(ctx, kv, l, q, block_tables, context_lens, m->attn, &pa,
-                                     max_ctx)))
+                                     max_ctx, &fusion)))
       return st;
     if ((st = lin(ctx, ly.w[KANSO_W_ATTN_OUTPUT], m->attn, m->proj, B, act_mode))) return st;
     if ((st = launch_residual_add(ctx, m->hidden, m->proj, (int64_t)B * hidden))) return st;

@@ -40,6 +40,17 @@ struct PaArgs {
   float scale;
   int* status;
   uint32_t* tickets;  // [seq][kv head], zero between calls; nullptr = separate stage-2 launch
+  // Decode-step fusion (src/model.rs:1141-1207), off when k_new is nullptr: q arrives
+  // un-rotated and is rotated as it is staged; the CTA whose partition holds the newest token
+  // (position context_len - 1) rotates that token's K, quantises K and V and stores them in
+  // the pool slot slots[seq] before it reads the partition.
+  const float* k_new;  // [seq][kv head][hd]
+  const float* v_new;
+  const uint32_t* positions;
+  const uint32_t* slots;
+  const float* cos_t;  // [table_len][hd / 2]
+  const float* sin_t;
+  int table_len;
 };
 
 __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
@@ -48,19 +59,31 @@ __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
   return __uint_as_float(bits) - 8388736.0f;  // 2^23 + 128
 }
 
-template <int G>
-__global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) {
+// NT = threads per CTA.
+template <int G, int NT>
+__global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_launch_dependents();
-  pdl_wait();  // q, the table and the pool rows of the new token come from earlier kernels
   const uint32_t hd = a.g.head_dim, bs = a.g.block_size;
   const uint32_t part = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-  const uint32_t ctx = a.lens[seq];
+  // Inside the decode step (fused mode) the context lengths, positions, slots and the block
+  // table are inputs of the whole step, written before its first kernel: they are read before
+  // the wait, and only q and the new K/V rows, which the previous kernel produces, after it.
+  const bool fused = a.k_new != nullptr;
+  uint32_t ctx = 0, pos = 0;
+  if (fused) {
+    ctx = a.lens[seq];
+    pos = a.positions[seq];
+  }
+  if (!fused) {
+    pdl_wait();  // q, the table and the lengths may come from earlier kernels
+    ctx = a.lens[seq];
+  }
   const uint32_t t0 = part * a.part_tokens;
   if (ctx == 0 && a.tickets && part == 0) {
     // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
     float* o = a.out + ((size_t)seq * a.num_heads + (size_t)kvh * G) * hd;
-    for (uint32_t e = threadIdx.x; e < G * hd; e += PA_THREADS) o[e] = 0.f;
+    for (uint32_t e = threadIdx.x; e < G * hd; e += NT) o[e] = 0.f;
   }
   if (t0 >= ctx) return;
   const uint32_t n = min(a.part_tokens, ctx - t0);
@@ -75,32 +98,12 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
   float* vscs = prob + ((G * a.part_tokens + 3) & ~3u);      // [part_tokens] V scales
   float* red = vscs + ((a.part_tokens + 3) & ~3u);           // PV scratch, 16-byte aligned
-  __shared__ float s_red[32];
 
-  // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
+  // physical blocks of this partition (bounds-checked once)
   {
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int gq = warp; gq < G; gq += PA_THREADS / 32) {
-      const float* qrow = a.q + ((size_t)seq * a.num_heads + (size_t)kvh * G + gq) * hd;
-      float amax = 0.f;
-      for (uint32_t d = lane; d < hd; d += 32) amax = fmaxf(amax, fabsf(qrow[d]));
-#pragma unroll
-      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-      float d_ = amax / 127.0f;
-      float id = d_ != 0.f ? 1.0f / d_ : 0.f;
-      for (uint32_t d = lane; d < hd; d += 32) {
-        float x = qrow[d];
-        float h = fminf(fmaxf(rintf(x * id), -127.f), 127.f);
-        float l = fminf(fmaxf(rintf(fmaf(-d_, h, x) * (254.0f * id)), -127.f), 127.f);
-        qhi[gq * hd + d] = (int8_t)h;
-        qlo[gq * hd + d] = (int8_t)l;
-      }
-      if (lane == 0) qd[gq] = d_ * (1.0f / 254.0f);
-    }
-    // physical blocks of this partition (bounds-checked once)
     const uint32_t first_blk = t0 / bs;
     const uint32_t last_blk = (t0 + n - 1) / bs;
-    for (uint32_t b = first_blk + tid; b <= last_blk; b += PA_THREADS) {
+    for (uint32_t b = first_blk + tid; b <= last_blk; b += NT) {
       uint32_t phys = a.tables[(size_t)seq * a.max_blocks + b];
       if (phys >= a.g.num_blocks) {
         atomicOr(a.status, DEV_BAD_INDEX);
@@ -109,15 +112,34 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
       blk[b - first_blk] = phys;
     }
   }
-  __syncthreads();
+  // RoPE factors of this sequence's position, and the pool slot of its newest token
+  __shared__ float s_cos[PA_MAX_HEAD_DIM / 2], s_sin[PA_MAX_HEAD_DIM / 2];
+  uint32_t new_slot = 0;
+  if (fused) {
+    if (pos >= (uint32_t)a.table_len) {
+      if (tid == 0) atomicOr(a.status, DEV_BAD_INDEX);
+      pos = 0;
+    }
+    for (uint32_t j = tid; j < hd / 2; j += NT) {
+      s_cos[j] = a.cos_t[(size_t)pos * (hd / 2) + j];
+      s_sin[j] = a.sin_t[(size_t)pos * (hd / 2) + j];
+    }
+    new_slot = a.slots[seq];
+  }
+  __syncthreads();  // block ids and RoPE factors are in shared memory
   const uint32_t first_blk = t0 / bs;
+  // position of the newest token inside this partition (fused mode), else out of range
+  const uint32_t i_new = (fused && ctx - 1 >= t0 && ctx - 1 < t0 + n) ? ctx - 1 - t0 : 0xFFFFFFFFu;
+  __shared__ __align__(16) int8_t s_newk[PA_MAX_HEAD_DIM], s_newv[PA_MAX_HEAD_DIM];
+  __shared__ float s_newsc[2];
 
-  // PV tiling: thread = (8 dims = one 64-bit word c of the V row, token slice). The loads of a
-  // thread's first four tokens are issued here, before the QK phase, so that short partitions
-  // pay one trip to memory for K and V together; later groups of four are loaded one group
-  // ahead of their use.
+  // The cache rows of earlier steps do not depend on the kernel before this one either: the
+  // first K row of every thread, its scales, and the first four V words of every thread are
+  // requested here, before the wait.
+  // PV tiling: thread = (8 dims = one 64-bit word c of the V row, token slice); later groups of
+  // four tokens are loaded one group ahead of their use.
   const uint32_t dwords = hd / 8;
-  const uint32_t nslice = PA_THREADS / dwords;  // hd in {16..256} -> dwords in {2..32}
+  const uint32_t nslice = NT / dwords;  // hd in {16..256} -> dwords in {2..32}
   const uint32_t c = tid % dwords, slice = tid / dwords;
   auto load_v = [&](uint32_t i0, uint2 (&vw)[4]) {
 #pragma unroll
@@ -126,8 +148,12 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
       if (i < n) {
         const uint32_t t = t0 + i;
         const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-        vw[j] = __ldg(reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(t % bs) * hd) +
-                      c);
+        const uint2* vp =
+            reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(t % bs) * hd) + c;
+        if (i == i_new)
+          vw[j] = reinterpret_cast<const uint2*>(s_newv)[c];  // stored by this CTA a moment ago
+        else
+          vw[j] = __ldg(vp);
       } else {
         vw[j] = make_uint2(0u, 0u);
       }
@@ -135,27 +161,162 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   };
   uint2 vcur[4];
   load_v(slice, vcur);
+  const uint32_t nchunk = hd / 16;
+  uint4 kpre[4];
+  float kscp = 0.f, vscp = 0.f;
+  if ((uint32_t)tid < n) {
+    const uint32_t t = t0 + tid;
+    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
+    const uint32_t off = t % bs;
+    const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      kpre[j] = (uint32_t)j < nchunk ? __ldg(krow + j) : make_uint4(0, 0, 0, 0);
+    kscp = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
+    vscp = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
+  }
+  if (fused) pdl_wait();  // q and the new K/V rows come from the kernel before this one
+
+  // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    const uint32_t half = hd / 2;
+    const float* cs = s_cos;
+    const float* sn = s_sin;
+    // element d of a head after rotate-half RoPE; multiplies and adds round separately, as
+    // the reference's tensor ops do (the stored K bytes must equal the CPU path's)
+    auto roped = [&](const float* row, uint32_t d) {
+      if (!fused) return row[d];
+      const uint32_t j = d < half ? d : d - half;
+      const float x0 = row[j], x1 = row[j + half], c_ = cs[j], s_ = sn[j];
+      return d < half ? __fsub_rn(__fmul_rn(x0, c_), __fmul_rn(x1, s_))
+                      : __fadd_rn(__fmul_rn(x0, s_), __fmul_rn(x1, c_));
+    };
+    for (int gq = warp; gq < G; gq += NT / 32) {
+      const float* qrow = a.q + ((size_t)seq * a.num_heads + (size_t)kvh * G + gq) * hd;
+      constexpr int QE = PA_MAX_HEAD_DIM / 32;
+      float qe[QE];  // this lane's elements of the head, loaded (and rotated) once
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < QE; ++i) {
+        const uint32_t d = lane + 32 * i;
+        qe[i] = d < hd ? roped(qrow, d) : 0.f;
+        amax = fmaxf(amax, fabsf(qe[i]));
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      float d_ = amax / 127.0f;
+      float id = d_ != 0.f ? 1.0f / d_ : 0.f;
+#pragma unroll
+      for (int i = 0; i < QE; ++i) {
+        const uint32_t d = lane + 32 * i;
+        if (d < hd) {
+          float x = qe[i];
+          float h = fminf(fmaxf(rintf(x * id), -127.f), 127.f);
+          float l = fminf(fmaxf(rintf(fmaf(-d_, h, x) * (254.0f * id)), -127.f), 127.f);
+          qhi[gq * hd + d] = (int8_t)h;
+          qlo[gq * hd + d] = (int8_t)l;
+        }
+      }
+      if (lane == 0) qd[gq] = d_ * (1.0f / 254.0f);
+    }
+    // the newest token's K (warp 0) and V (warp 1) into the pool, by the CTA that reads them
+    // (quantize_head_slice, src/kv_cache/quantized_storage.rs:452-469)
+    if (fused && warp < 2 && ctx - 1 >= t0 && ctx - 1 < t0 + n) {
+      const bool is_k = warp == 0;
+      const float* src = (is_k ? a.k_new : a.v_new) + ((size_t)seq * a.g.kv_heads + kvh) * hd;
+      const uint32_t sl = new_slot;
+      const uint32_t block = sl / bs, off = sl % bs;
+      if (block >= a.g.num_blocks) {
+        if (lane == 0) atomicOr(a.status, DEV_BAD_INDEX);
+      } else {
+        constexpr int MAXE = PA_MAX_HEAD_DIM / 32;
+        float e[MAXE];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXE; ++i) {
+          const uint32_t d = lane + 32 * i;
+          e[i] = 0.f;
+          if (d < hd) {
+            e[i] = is_k ? roped(src, d) : src[d];
+            amax = fmaxf(amax, fabsf(e[i]));
+          }
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        const float inv = __fdiv_rn(1.0f, scale);
+        uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, block, kvh);
+        int8_t* dst =
+            reinterpret_cast<int8_t*>(rec + (is_k ? a.g.k_off() : a.g.v_off())) + (size_t)off * hd;
+        int8_t* mine = is_k ? s_newk : s_newv;  // this CTA reads the row back from here
+#pragma unroll
+        for (int i = 0; i < MAXE; ++i) {
+          const uint32_t d = lane + 32 * i;
+          if (d < hd) {
+            const int8_t qv = (int8_t)fminf(fmaxf(roundf(__fmul_rn(e[i], inv)), -127.f), 127.f);
+            dst[d] = qv;
+            mine[d] = qv;
+          }
+        }
+        if (lane == 0) {
+          reinterpret_cast<float*>(rec + (is_k ? a.g.ks_off() : a.g.vs_off()))[off] = scale;
+          s_newsc[is_k ? 0 : 1] = scale;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // the newest token's row was requested before it existed: take it from shared memory
+  if (i_new != 0xFFFFFFFFu) {
+    if ((uint32_t)tid == i_new) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if ((uint32_t)j < nchunk) kpre[j] = reinterpret_cast<const uint4*>(s_newk)[j];
+      kscp = s_newsc[0];
+      vscp = s_newsc[1];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (slice + j * nslice == i_new) vcur[j] = reinterpret_cast<const uint2*>(s_newv)[c];
+  }
 
   // --- QK: one thread per token
   float lmax[G];
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) lmax[gq] = -INFINITY;
-  for (uint32_t i = tid; i < n; i += PA_THREADS) {
+  for (uint32_t i = tid; i < n; i += NT) {
     const uint32_t t = t0 + i;
     const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
     const uint32_t off = t % bs;
+    const bool first = i == (uint32_t)tid;  // this thread's first token: row already here
     const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
-    const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
-    vscs[i] = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
+    const uint4* knew = reinterpret_cast<const uint4*>(s_newk);
+    float ksc, vsc_i;
+    if (first) {
+      ksc = kscp;
+      vsc_i = vscp;
+    } else if (i == i_new) {
+      ksc = s_newsc[0];
+      vsc_i = s_newsc[1];
+    } else {
+      ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
+      vsc_i = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
+    }
+    vscs[i] = vsc_i;
     int ih[G], il[G];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) ih[gq] = il[gq] = 0;
-    const uint32_t nchunk = hd / 16;
     for (uint32_t c0 = 0; c0 < nchunk; c0 += 4) {
       uint4 kw4[4];  // four chunks of the row in flight (head_dim 16 and 32 have fewer)
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        kw4[j] = c0 + j < nchunk ? __ldg(krow + c0 + j) : make_uint4(0, 0, 0, 0);
+      for (int j = 0; j < 4; ++j) {
+        if (first && c0 == 0)
+          kw4[j] = kpre[j];
+        else
+          kw4[j] = c0 + j < nchunk ? (i == i_new ? knew[c0 + j] : __ldg(krow + c0 + j))
+                                   : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (c0 + j >= nchunk) break;
@@ -183,13 +344,27 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
       lmax[gq] = fmaxf(lmax[gq], sc);
     }
   }
-  // --- softmax inside the partition
+  // --- softmax inside the partition; the G heads share each block-wide reduction
+  __shared__ float s_redm[PA_MAX_GROUP * (NT / 32)], s_reds[PA_MAX_GROUP * (NT / 32)];
+  const int warp_i = tid >> 5, lane_i = tid & 31;
   float pmax[G], psum[G];
 #pragma unroll
-  for (int gq = 0; gq < G; ++gq) pmax[gq] = block_max(lmax[gq], s_red);
+  for (int gq = 0; gq < G; ++gq) {
+    float m = lmax[gq];
 #pragma unroll
-  for (int gq = 0; gq < G; ++gq) psum[gq] = 0.f;
-  for (uint32_t i = tid; i < n; i += PA_THREADS) {
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_i == 0) s_redm[gq * (NT / 32) + warp_i] = m;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) {
+    float m = s_redm[gq * (NT / 32)];
+#pragma unroll
+    for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, s_redm[gq * (NT / 32) + w]);
+    pmax[gq] = m;
+    psum[gq] = 0.f;
+  }
+  for (uint32_t i = tid; i < n; i += NT) {
     const float vsc = vscs[i];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) {
@@ -199,8 +374,20 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
     }
   }
 #pragma unroll
-  for (int gq = 0; gq < G; ++gq) psum[gq] = block_sum(psum[gq], s_red);
-  __syncthreads();
+  for (int gq = 0; gq < G; ++gq) {
+    float t = psum[gq];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+    if (lane_i == 0) s_reds[gq * (NT / 32) + warp_i] = t;
+  }
+  __syncthreads();  // also: every probability is written before PV reads them
+#pragma unroll
+  for (int gq = 0; gq < G; ++gq) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) t += s_reds[gq * (NT / 32) + w];
+    psum[gq] = t;
+  }
 
   // --- PV
   float acc[G][8];
@@ -243,13 +430,25 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
         make_float4(acc[gq][4], acc[gq][5], acc[gq][6], acc[gq][7]);
   }
   __syncthreads();
-  for (uint32_t e = tid; e < G * hd; e += PA_THREADS) {
+  // partitions that exist in this grid (a context longer than the host said is cut off there)
+  const uint32_t np = min((ctx + a.part_tokens - 1) / a.part_tokens, a.num_parts);
+  const bool single = a.tickets && np == 1;  // the only partition: normalise and finish here
+  for (uint32_t e = tid; e < G * hd; e += NT) {
     float s = 0.f;
     for (uint32_t sl = 0; sl < nslice; ++sl) s += red[sl * G * hd + e];
     const uint32_t gq = e / hd, d = e % hd;
     const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
-    a.part_acc[(head * a.num_parts + part) * hd + d] = s;
+    if (single) {
+      float l = 0.f;
+#pragma unroll
+      for (int k = 0; k < G; ++k)
+        if (k == (int)gq) l = psum[k];
+      a.out[head * hd + d] = l > 0.f ? s / l : 0.f;
+    } else {
+      a.part_acc[(head * a.num_parts + part) * hd + d] = s;
+    }
   }
+  if (single) return;
   if (tid < G) {
     const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + tid;
     float m = 0.f, l = 0.f;
@@ -266,8 +465,6 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
 
   // --- merge, by the CTA that draws the last ticket of this (sequence, kv head)
   __shared__ uint32_t s_last;
-  // partitions that exist in this grid (a context longer than the host said is cut off there)
-  const uint32_t np = min((ctx + a.part_tokens - 1) / a.part_tokens, a.num_parts);
   __threadfence();  // this CTA's partials are visible device-wide before its ticket is
   __syncthreads();
   if (tid == 0) {
@@ -279,37 +476,36 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_stage1(const PaArgs a) 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // weights e^{m_p - M} per (head, partition) into shared memory (the probabilities are dead)
-  float* wts = prob;               // [G][np], np <= part_tokens (checked by the host)
-  float* invs = vscs;              // [G]
-  {
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int gq = warp; gq < G; gq += PA_THREADS / 32) {
-      const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
-      const float* ml = a.part_ml + head * a.num_parts * 2;
-      float M = -INFINITY;
-      for (uint32_t p = lane; p < np; p += 32) M = fmaxf(M, __ldcg(ml + 2 * p));
-#pragma unroll
-      for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
-      float denom = 0.f;
-      for (uint32_t p = lane; p < np; p += 32) {
-        const float w = expf(__ldcg(ml + 2 * p) - M);
-        wts[gq * np + p] = w;
-        denom += __ldcg(ml + 2 * p + 1) * w;
-      }
-#pragma unroll
-      for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xFFFFFFFFu, denom, o);
-      if (lane == 0) invs[gq] = denom > 0.f ? 1.0f / denom : 0.f;
-    }
-  }
-  __syncthreads();
-  for (uint32_t e = tid; e < G * hd; e += PA_THREADS) {
+  // Each thread merges its output elements on its own: the (max, sum) pairs and the
+  // accumulators of up to 16 partitions are requested together (one trip to L2), then folded
+  // in with the running-maximum form of the softmax merge.
+  for (uint32_t e = tid; e < G * hd; e += NT) {
     const uint32_t gq = e / hd, d = e % hd;
     const size_t head = (size_t)seq * a.num_heads + (size_t)kvh * G + gq;
+    const float* ml = a.part_ml + head * a.num_parts * 2;
     const float* pa = a.part_acc + head * a.num_parts * hd + d;
-    float s = 0.f;
-    for (uint32_t p = 0; p < np; ++p) s += __ldcg(pa + (size_t)p * hd) * wts[gq * np + p];
-    a.out[head * hd + d] = s * invs[gq];
+    float M = -INFINITY, s = 0.f, l = 0.f;
+    for (uint32_t p0 = 0; p0 < np; p0 += 16) {
+      float2 mlv[16];
+      float av[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const uint32_t pp = min(p0 + k, np - 1);
+        mlv[k] = __ldcg(reinterpret_cast<const float2*>(ml) + pp);
+        av[k] = __ldcg(pa + (size_t)pp * hd);
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        if (p0 + k < np) {
+          const float Mn = fmaxf(M, mlv[k].x);
+          const float so = expf(M - Mn), sn = expf(mlv[k].x - Mn);
+          s = s * so + av[k] * sn;
+          l = l * so + mlv[k].y * sn;
+          M = Mn;
+        }
+      }
+    }
+    a.out[head * hd + d] = l > 0.f ? s / l : 0.f;
   }
 }
 
@@ -372,9 +568,10 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
 
 // Dynamic shared memory of stage 1: query planes and scales, block ids, probabilities,
 // V scales, PV reduction scratch.
-static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t block_size) {
+static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t block_size,
+                             uint32_t threads) {
   const uint32_t nblk_part = ((pt + block_size - 1) / block_size + 4) & ~3u;
-  const uint32_t dwords = hd / 8, nslice = PA_THREADS / dwords;
+  const uint32_t dwords = hd / 8, nslice = threads / dwords;
   size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4 +
                 (size_t)((pt + 3) & ~3u) * 4;
   size_t red_bytes = (size_t)nslice * G * hd * 4;
@@ -382,23 +579,27 @@ static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t bloc
   return smem + red_bytes;
 }
 
-template <int G>
-static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
+template <int G, int NT>
+static void launch_stage1_nt(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
   static size_t smem_set[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (smem > smem_set[dev & 15]) {
-    cudaFuncSetAttribute(paged_attn_stage1<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(paged_attn_stage1<G, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     smem_set[dev & 15] = smem;
   }
-  launch_dependent(ctx, paged_attn_stage1<G>, grid, dim3(PA_THREADS), smem, a);
+  launch_dependent(ctx, paged_attn_stage1<G, NT>, grid, dim3(NT), smem, a);
+}
+template <int G>
+static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
+  launch_stage1_nt<G, PA_THREADS>(ctx, a, grid, smem);
 }
 
 int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
                                const float* q, const uint32_t* tables, const uint32_t* lens,
                                float* out, const kanso_paged_attention_params* p,
-                               uint32_t max_ctx_hint) {
+                               uint32_t max_ctx_hint, const PaDecodeFusion* fusion) {
   KvGeom g = kv_geom(kv);
   const uint32_t G = p->num_heads / p->num_kv_heads;
   const uint32_t hd = p->head_dim;
@@ -412,7 +613,6 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   // whole blocks per partition keep the per-partition block list simple
   if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
-
   const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
   const size_t acc_bytes = nheads_total * nparts * hd * sizeof(float);
   const size_t ml_bytes = nheads_total * nparts * 2 * sizeof(float);
@@ -439,8 +639,20 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   const bool merge_in_stage1 =
       (uint64_t)p->num_seqs * p->num_kv_heads <= kanso_cuda_ctx::kPaTickets && nparts <= pt;
   a.tickets = merge_in_stage1 ? ctx->pa_tickets : nullptr;
+  a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
+  a.positions = a.slots = nullptr;
+  a.table_len = 0;
+  if (fusion) {
+    a.k_new = fusion->k_new;
+    a.v_new = fusion->v_new;
+    a.positions = fusion->positions;
+    a.slots = fusion->slots;
+    a.cos_t = fusion->cos_t;
+    a.sin_t = fusion->sin_t;
+    a.table_len = fusion->table_len;
+  }
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size);
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, PA_THREADS);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: %zu bytes of shared memory needed",
                 smem);
@@ -511,7 +723,7 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
     }
   }
   return launch_paged_attention(ctx, kv, layer, q, block_tables, context_lens, out, params,
-                                max_ctx);
+                                max_ctx, nullptr);
 }
 
 }  // extern "C"
@@ -608,8 +820,11 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.scale = p->scale;
   a.status = ctx->dev_status;
   a.tickets = nullptr;  // two launches: stage 2 merges
+  a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
+  a.positions = a.slots = nullptr;
+  a.table_len = 0;
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size);
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, PA_THREADS);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "paged_attention_noalloc: %zu bytes of shared memory needed", smem);

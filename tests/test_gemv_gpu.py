@@ -116,6 +116,21 @@ def test_few_row_gemm(ctx, kb, oracle, torch_cuda, M):
                    oracle.gemm_q4_k(b4, x, M, N, K)) <= TOL
 
 
+@pytest.mark.parametrize("N,K", [(50, 64), (17, 4096), (960, 2560), (2560, 960), (33, 14336)])
+@pytest.mark.parametrize("M", [2, 5, 8])
+def test_q8_0_tensor_core_gemv_edges(ctx, kb, oracle, torch_cuda, M, N, K):
+    """The int8-MMA kernel's corners: row counts that are not a multiple of its 16-row groups,
+    rows split across CTAs (K > 1024: partial sums added with atomics), one and two planes."""
+    rng = np.random.Generator(np.random.PCG64(0xB2000700 + 131 * M + N + K))
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b8 = oracle.quantize_weights_q8_0(w)
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, b8, x, M, N, K),
+                   oracle.gemm_q8_0(b8, x, M, N, K)) <= TOL
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q8_0, b8, x, M, N, K, kb.ACT_Q8),
+                   oracle.gemm_q8_0(b8, x, M, N, K, 1)) <= 1e-5
+
+
 def test_linearity_at_full_size(ctx, kb, oracle, torch_cuda):
     """Size-independent property at the benchmark shape: W(ax + by) = a Wx + b Wy."""
     torch = torch_cuda
