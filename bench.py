@@ -186,6 +186,153 @@ def run_reference(args):
     }))
 
 
+def _graph_time_us(torch, stream, fn, calls_per_graph, iters=20):
+    """Average device time of one call of a step captured in a CUDA graph (CUDA events)."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        g.replay()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * calls_per_graph)
+
+
+def _random_blocks(torch, kb, dtype, rows, cols, copies):
+    """Random block bytes with a sane f16 scale: timing only, the values are never checked."""
+    blk, per = (34, 32) if dtype == kb.DTYPE_Q8_0 else (144, 256)
+    out = []
+    for _ in range(copies):
+        w = torch.randint(0, 255, (rows * cols // per * blk,), dtype=torch.uint8, device="cuda")
+        v = w.view(-1, blk)
+        v[:, 1] = 0x1C
+        if dtype != kb.DTYPE_Q8_0:
+            v[:, 3] = 0x1C
+        out.append(w)
+    return out
+
+
+def other_paths(torch, kb, ctx, stream, decode_batches=(1, 8, 32, 64), decode_only=False):
+    """The other rows of the hot path, timed the same way (graph + events, weights rotated
+    through more than the L2's 126 MB): cfg 1 Q8_0 GEMV, cfg 3 batched GEMM, cfg 4 decode."""
+    res = {}
+    if decode_only:
+        res["cfg4_decode_smollm2_360m_q8_0"] = decode_rates(torch, kb, ctx, stream, decode_batches)
+        return res
+    gemv = {}
+    for rows, cols in ((2560, 960), (960, 2560)):
+        nbytes = rows * cols // 32 * 34
+        copies = max(2, min(256, int(400e6 / nbytes)))
+        ws = _random_blocks(torch, kb, kb.DTYPE_Q8_0, rows, cols, copies)
+        x = torch.randn(1, cols, device="cuda")
+        y = torch.empty(1, rows, device="cuda")
+
+        def step():
+            for w in ws:
+                ctx.gemm_q8_0(w, x, y, 1, rows, cols, kb.ACT_F32)
+        us = _graph_time_us(torch, stream, step, copies)
+        gemv[f"{rows}x{cols}"] = {"us_per_launch": us, "GB/s": nbytes / us / 1e3}
+    res["cfg1_q8_0_gemv_batch1"] = gemv
+    gemm = {}
+    for name, dtype in (("q8_0", kb.DTYPE_Q8_0), ("q4_k", kb.DTYPE_Q4_K)):
+        rows, cols = 14336, 4096
+        nbytes = rows * cols // (32 if dtype == kb.DTYPE_Q8_0 else 256) * (34 if dtype == kb.DTYPE_Q8_0 else 144)
+        copies = max(2, int(300e6 / nbytes))
+        ws = _random_blocks(torch, kb, dtype, rows, cols, copies)
+        for M in (8, 32, 128):
+            x = torch.randn(M, cols, device="cuda")
+            y = torch.empty(M, rows, device="cuda")
+            f = ctx.gemm_q8_0 if dtype == kb.DTYPE_Q8_0 else ctx.gemm_q4_k
+
+            def step():
+                for w in ws:
+                    f(w, x, y, M, rows, cols, kb.ACT_F32)
+            us = _graph_time_us(torch, stream, step, copies, iters=5)
+            gemm[f"{name}_M{M}_N{rows}_K{cols}"] = {
+                "us_per_call": us, "TFLOP/s": 2 * M * rows * cols / us / 1e6,
+                "weight_GB/s": nbytes / us / 1e3}
+    res["cfg3_batched_gemm"] = gemm
+    res["cfg4_decode_smollm2_360m_q8_0"] = decode_rates(torch, kb, ctx, stream, decode_batches)
+    return res
+
+
+def decode_rates(torch, kb, ctx, stream, batches=(1, 8, 32, 64)):
+    """cfg 4: one decode step of the SmolLM2-360M architecture, Q8_0 weights (random block
+    bytes), int8 paged KV with 16-token blocks and permuted block tables, contexts uniform in
+    [256, 4096]; tokens per second = sequences / step time."""
+    L, hidden, H, KH, inter, vocab, bs = 32, 960, 15, 5, 2560, 49152, 16
+    hd = hidden // H
+    cfg = kb.ModelConfig(hidden, H, KH, L, inter, vocab, bs, 4352, 1e-5, 100000.0)
+    m = kb.Model(ctx, cfg)
+    rng = np.random.Generator(np.random.PCG64(SEED + 40))
+
+    def qblocks(rows, cols):
+        b = rng.integers(0, 256, size=(rows * cols // 32, 34), dtype=np.uint8)
+        b[:, 0] = 0x00
+        b[:, 1] = 0x14  # f16 scale ~ 0.00098
+        return b.reshape(-1)
+    shapes = {0: (H * hd, hidden), 1: (KH * hd, hidden), 2: (KH * hd, hidden), 3: (hidden, H * hd),
+              4: (inter, hidden), 5: (inter, hidden), 6: (hidden, inter)}
+    for l in range(L):
+        for which, (r, c) in shapes.items():
+            m.set_weight(l, which, qblocks(r, c), kb.DTYPE_Q8_0, r, c)
+        m.set_norm(l, 0, np.ones(hidden, np.float32))
+        m.set_norm(l, 1, np.ones(hidden, np.float32))
+    m.set_weight(0, 7, qblocks(vocab, hidden), kb.DTYPE_Q8_0, vocab, hidden)
+    m.set_norm(0, 2, np.ones(hidden, np.float32))
+    out = {}
+    for B in batches:
+        lens = rng.integers(256, 4097, size=B)
+        nblk = [(int(c) + bs - 1) // bs for c in lens]
+        NB = sum(nblk) + 8
+        pool = kb.KvPool(ctx, L, NB, bs, KH, hd)
+        perm = rng.permutation(NB)
+        maxb = max(nblk)
+        tables = np.zeros((B, maxb), np.uint32)
+        used, hist = 0, []
+        for i in range(B):
+            blocks = perm[used:used + nblk[i]]
+            used += nblk[i]
+            tables[i, :nblk[i]] = blocks
+            tables[i, nblk[i]:] = blocks[-1]
+            t = np.arange(int(lens[i]) - 1)
+            hist.append((blocks[t // bs] * bs + t % bs).astype(np.uint32))
+        hist = np.concatenate(hist)
+        hs = torch.from_numpy(hist.astype(np.int64)).to(torch.int32).cuda()
+        for l in range(L):
+            k = torch.randn(len(hist), KH * hd, device="cuda")
+            v = torch.randn(len(hist), KH * hd, device="cuda")
+            pool.write_slots(l, hs, k, v, len(hist))
+        ctx.sync()
+        tok = torch.from_numpy(rng.integers(0, vocab, size=B).astype(np.int32)).cuda()
+        pos = torch.from_numpy((lens - 1).astype(np.int32)).cuda()
+        slot = torch.from_numpy(np.array(
+            [tables[i, (lens[i] - 1) // bs] * bs + (lens[i] - 1) % bs for i in range(B)],
+            np.int32)).cuda()
+        tb = torch.from_numpy(tables.astype(np.int32)).cuda()
+        ln = torch.from_numpy(lens.astype(np.int32)).cuda()
+        logits = torch.empty(B, vocab, device="cuda")
+
+        def step():
+            m.decode_step_device(pool, tok, pos, slot, tb, ln, B, maxb, int(lens.max()), logits)
+        l0 = ctx.launches
+        step()
+        ctx.sync()
+        launches = ctx.launches - l0
+        us = _graph_time_us(torch, stream, step, 1)
+        out[f"B{B}"] = {"tok/s": B / us * 1e6, "us_per_step": us, "sum_ctx": int(lens.sum()),
+                        "launches_per_step": int(launches)}
+        pool.destroy()
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -377,6 +524,9 @@ def run_ours(args):
     }
     if cpu:
         line["cpu_baseline"] = cpu
+    if world == 1 and not os.environ.get("KANSO_BENCH_SKIP_EXTRAS"):
+        # not part of the headline value: the remaining rows of the path, for the record
+        line["other_paths"] = other_paths(torch, kb, ctx, stream)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -389,7 +539,43 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pairs", type=int, default=8, help="distinct (up, down) pairs in the ring")
+    ap.add_argument("--decode-only", default=None, metavar="B[,B...]",
+                    help="time only the decode step at these batch sizes (1 GPU) and print them; "
+                         "for profiler captures of that path")
+    ap.add_argument("--gemm-only", default=None, metavar="FMT,M",
+                    help="run only the cfg 3 GEMM (q8_0 or q4_k, N=14336, K=4096) with M activation "
+                         "rows over four weight copies, eagerly; for profiler captures of that path")
     args = ap.parse_args()
+    if args.gemm_only:
+        import torch
+        kb = importlib.import_module("kanso-infer_b200").backend
+        torch.cuda.set_device(0)
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        ctx = kb.Context(0, stream)
+        fmt, M = args.gemm_only.split(",")
+        M = int(M)
+        dtype = kb.DTYPE_Q8_0 if fmt == "q8_0" else kb.DTYPE_Q4_K
+        ws = _random_blocks(torch, kb, dtype, 14336, 4096, 4)
+        x = torch.randn(M, 4096, device="cuda")
+        y = torch.empty(M, 14336, device="cuda")
+        for w in ws:
+            (ctx.gemm_q8_0 if dtype == kb.DTYPE_Q8_0 else ctx.gemm_q4_k)(w, x, y, M, 14336, 4096,
+                                                                         kb.ACT_F32)
+        ctx.sync()
+        print(json.dumps({"gemm_only": args.gemm_only, "launches": int(ctx.launches)}))
+        return
+    if args.decode_only:
+        import torch
+        kb = importlib.import_module("kanso-infer_b200").backend
+        torch.cuda.set_device(0)
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        ctx = kb.Context(0, stream)
+        ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 1)
+        batches = tuple(int(b) for b in args.decode_only.split(","))
+        print(json.dumps(other_paths(torch, kb, ctx, stream, batches, decode_only=True)))
+        return
     if args.impl == "reference":
         if args.steps > 50:
             args.steps = 50  # bounded sample: the CPU step takes ~0.1 s
