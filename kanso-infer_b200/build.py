@@ -62,7 +62,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
             list(ex.map(run, jobs))
     objs = [os.path.join(OBJ, s[:-3] + ".o") for s in srcs]
     if jobs or force or not os.path.exists(LIB):
-        run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+        # -z defs: a symbol that no object defines fails the build here, not the first dlopen
+        run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+             "-Xlinker", "-z", "-Xlinker", "defs"])
     return LIB
 
 

@@ -42,23 +42,30 @@ constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
 constexpr int TC_A_PLANE = TC_TILE_N * TC_KC * 2;  // bytes of one f16 A term per stage (16 KB)
 constexpr int TC_A_STAGE = 2 * TC_A_PLANE;         // hi and lo terms
 
+constexpr int TC_MAX_SEGS = 3;  // matrices of one launch that share the activations (Q, K, V)
+
 struct TcArgs {
-  const uint8_t* w;
+  const uint8_t* w[TC_MAX_SEGS];
+  float* y[TC_MAX_SEGS];          // [M, N] each
+  int64_t N[TC_MAX_SEGS];
+  int tile_begin[TC_MAX_SEGS];    // first CTA (along x) of each matrix
+  int nseg;
   const __half* xp;  // packed activations [K/64][8][Mt][8]
-  float* y;
-  int64_t N;
+  const float* resid;  // ksplit == 1: y = resid + W.x (may alias y); nullptr: plain store
   int K, M, Mt;      // Mt = M rounded up to 16
   int bpr;           // blocks (Q8_0) or super-blocks (Q4_K) per row
-  int ksplit;        // CTAs along K
+  int ksplit;        // CTAs along K; > 1: partial sums are added into y with atomics
   int stages_total;  // K / 64
   int nstage_smem;   // shared-memory stages of the A/B tiles (2 or 3)
   int* status;
 };
 
+
 // x f32 [M,K] -> two f16 terms xh + xl, layout [stage][term][chunk of 8 k][row m][8 values];
 // rows >= M are zero.
-__global__ void tc_pack_activations_kernel(const float* __restrict__ x, __half* __restrict__ xp,
-                                           int M, int Mt, int K) {
+__global__ void tc_pack_activations_kernel(const float* __restrict__ x,
+                                           const float* __restrict__ x2,
+                                           __half* __restrict__ xp, int M, int Mt, int K) {
   const int64_t total = (int64_t)(K / 8) * Mt;  // one thread per (chunk, row)
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -68,7 +75,14 @@ __global__ void tc_pack_activations_kernel(const float* __restrict__ x, __half* 
     if (m < M) {
       const float4* src = reinterpret_cast<const float4*>(x + (int64_t)m * K + chunk * 8);
       const float4 a = src[0], b = src[1];
-      const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      if (x2) {  // the SwiGLU product feeding ffn_down: silu(x) * x2 (src/model.rs:367-382)
+        const float4* up = reinterpret_cast<const float4*>(x2 + (int64_t)m * K + chunk * 8);
+        const float4 c = up[0], d = up[1];
+        const float u[8] = {c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] / (1.0f + expf(-f[j])) * u[j];
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         hi[j] = __float2half_rn(f[j]);
@@ -188,22 +202,23 @@ struct TcRawCopy {
   bool on[kPerThread];
   int part;
 
-  __device__ __forceinline__ void init(const TcArgs& a, int64_t n0, int tid) {
+  __device__ __forceinline__ void init(const TcArgs& a, const uint8_t* w, int64_t N, int64_t n0,
+                                       int tid) {
     if (FMT == TC_FMT_Q8_0) {
 #pragma unroll
       for (int k = 0; k < kPerThread; ++k) {
         const int idx = tid + k * TC_PRODUCERS;
         on[k] = idx < TC_TILE_N * 17;
         const int row = min(idx / 17, TC_TILE_N - 1), word = idx - 17 * (idx / 17);
-        const int64_t n = min(n0 + row, a.N - 1);  // rows past N re-read the last row
-        src[k] = a.w + n * a.bpr * Q8_BYTES + 4 * word;
+        const int64_t n = min(n0 + row, N - 1);  // rows past N re-read the last row
+        src[k] = w + n * a.bpr * Q8_BYTES + 4 * word;
         dst[k] = row * TC_RAW_ROW_Q8 + 4 * word;
       }
     } else {
       on[0] = tid < 3 * TC_TILE_N;
       const int row = min(tid / 3, TC_TILE_N - 1);
       part = tid - 3 * (tid / 3);
-      src[0] = a.w + min(n0 + row, a.N - 1) * a.bpr * Q4K_BYTES;
+      src[0] = w + min(n0 + row, N - 1) * a.bpr * Q4K_BYTES;
       dst[0] = row * TC_RAW_ROW_Q4 + 16 * part;
     }
   }
@@ -331,7 +346,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint8_t* Raw = reinterpret_cast<uint8_t*>(done) + 96;  // 16-byte aligned
 
-  const int64_t n0 = (int64_t)blockIdx.x * TC_TILE_N;
+  int sg = 0;
+#pragma unroll
+  for (int i = 1; i < TC_MAX_SEGS; ++i)
+    if (i < a.nseg && (int)blockIdx.x >= a.tile_begin[i]) sg = i;
+  const int64_t n0 = (int64_t)((int)blockIdx.x - a.tile_begin[sg]) * TC_TILE_N;
+  const int64_t N = a.N[sg];
   const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
   const int s1 = (int)((int64_t)a.stages_total * (blockIdx.y + 1) / a.ksplit);
   uint32_t ncols = 32;
@@ -354,7 +374,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
   if (warp < TC_PRODUCERS / 32) {
     TcRawCopy<FMT> raw_copy;
-    raw_copy.init(a, n0, tid);
+    raw_copy.init(a, a.w[sg], N, n0, tid);
     const uint32_t raw_base = smem_u32(Raw);
     // one commit group per call, also when there is nothing left to copy, so that the
     // wait_group arithmetic below holds at the end of the K range
@@ -461,16 +481,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TC_PRODUCERS / 128) {
       uint32_t r[16];
       tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
-      if (n < a.N) {
+      if (n < N) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
           const int m = c16 * 16 + jj;
           if (m < a.M) {
-            float* dst = a.y + (int64_t)m * a.N + n;
+            float* dst = a.y[sg] + (int64_t)m * N + n;
+            const float v = __uint_as_float(r[jj]);
             if (a.ksplit == 1)
-              *dst = __uint_as_float(r[jj]);
+              *dst = a.resid ? a.resid[(int64_t)m * N + n] + v : v;
             else
-              atomicAdd(dst, __uint_as_float(r[jj]));
+              atomicAdd(dst, v);  // y holds zeros or the residual
           }
         }
       }
@@ -483,21 +504,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   if (warp == 0) tmem_dealloc(tmem_base, ncols);
 }
 
-// y[M,N] = x[M,K] @ W^T on the tensor cores; M up to 128 per call (larger M is chunked by
-// the caller). Sets *handled = false when the shape is outside this kernel's range.
-int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
-                  int64_t M, int64_t N, int64_t K, bool* handled) {
+// y_i[M,N_i] = x[M,K] @ W_i^T on the tensor cores for up to three matrices that share x, M up
+// to 128 per call (larger M is chunked by the caller). Optional fusions of the decode step:
+// x2 (activations are silu(x) * x2) and resid (y = resid + W.x, one matrix; may alias y).
+// Sets *handled = false (and launches nothing) when the shape is outside this kernel's range.
+int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void* const* w,
+                        float* const* y, const int64_t* rows, const float* x, const float* x2,
+                        const float* resid, int64_t M, int64_t K, bool* handled) {
   *handled = false;
   const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
-  if (M < 1 || M > 128 || N < 1 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
-  if (dtype == KANSO_DTYPE_Q8_0 && (reinterpret_cast<uintptr_t>(w) & 3) != 0) return KANSO_OK;
+  if (nseg < 1 || nseg > TC_MAX_SEGS || (resid && nseg != 1)) return KANSO_OK;
+  if (M < 1 || M > 128 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
+  if (!aligned16(x) || (x2 && !aligned16(x2))) return KANSO_OK;
+  int tiles_n = 0;
+  TcArgs a;
+  for (int i = 0; i < nseg; ++i) {
+    if (!w[i] || !y[i] || rows[i] < 1) return KANSO_OK;
+    if (dtype == KANSO_DTYPE_Q8_0 && (reinterpret_cast<uintptr_t>(w[i]) & 3) != 0) return KANSO_OK;
+    if (dtype == KANSO_DTYPE_Q4_K && !aligned16(w[i])) return KANSO_OK;
+    a.w[i] = (const uint8_t*)w[i];
+    a.y[i] = y[i];
+    a.N[i] = rows[i];
+    a.tile_begin[i] = tiles_n;
+    tiles_n += (int)((rows[i] + TC_TILE_N - 1) / TC_TILE_N);
+  }
+  for (int i = nseg; i < TC_MAX_SEGS; ++i) {
+    a.w[i] = a.w[0];
+    a.y[i] = a.y[0];
+    a.N[i] = a.N[0];
+    a.tile_begin[i] = tiles_n;
+  }
+  a.nseg = nseg;
   const int Mt = (int)((M + 15) / 16 * 16);
   const int stages_total = (int)(K / TC_KC);
-  const int tiles_n = (int)((N + TC_TILE_N - 1) / TC_TILE_N);
-  // split K until the grid covers the SMs about twice, keeping >= 4 stages per CTA
   // Split K only when the row tiles alone would leave more than half of the SMs idle: the
-  // partial sums of a split are added with atomics (after a clear of y), which costs more
-  // than an under-filled grid does. At least 4 stages stay in every CTA.
+  // partial sums of a split are added with atomics (onto the residual, or after a clear of
+  // y), which costs more than an under-filled grid does. At least 4 stages stay in every CTA.
   int ksplit = 1;
   while (tiles_n * ksplit * 2 <= ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
   const size_t xp_bytes = 2 * (size_t)(K / 8) * Mt * 16;
@@ -507,18 +549,27 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
 
   const int64_t chunks = (K / 8) * Mt;
   tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
-      x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
+      x, x2, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
   int32_t st = after_launch(ctx, "gemm_tc pack activations");
   if (st) return st;
-  if (ksplit > 1)
-    KANSO_CUDA_TRY(ctx, cudaMemsetAsync(y, 0, sizeof(float) * (size_t)M * N, ctx->stream),
-                   "gemm_tc: clear y");
-
-  TcArgs a;
-  a.w = (const uint8_t*)w;
+  a.resid = resid;
+  if (ksplit > 1) {
+    // the K slices add into y: y must hold the residual (in place) or zeros
+    a.resid = nullptr;
+    for (int i = 0; i < nseg; ++i) {
+      if (resid && resid == y[i]) continue;
+      if (resid)
+        KANSO_CUDA_TRY(ctx,
+                       cudaMemcpyAsync(y[i], resid, sizeof(float) * (size_t)M * rows[i],
+                                       cudaMemcpyDeviceToDevice, ctx->stream),
+                       "gemm_tc: residual copy");
+      else
+        KANSO_CUDA_TRY(ctx,
+                       cudaMemsetAsync(y[i], 0, sizeof(float) * (size_t)M * rows[i], ctx->stream),
+                       "gemm_tc: clear y");
+    }
+  }
   a.xp = reinterpret_cast<const __half*>(scratch);
-  a.y = y;
-  a.N = N;
   a.K = (int)K;
   a.M = (int)M;
   a.Mt = Mt;
@@ -548,6 +599,14 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   }
   kern<<<dim3(tiles_n, ksplit), TC_THREADS, smem, ctx->stream>>>(a);
   return after_launch(ctx, "gemm_tc");
+}
+
+int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
+                  int64_t M, int64_t N, int64_t K, bool* handled) {
+  const void* w1[1] = {w};
+  float* y1[1] = {y};
+  const int64_t r1[1] = {N};
+  return tc_matmul_multi(ctx, dtype, 1, w1, y1, r1, x, nullptr, nullptr, M, K, handled);
 }
 
 }  // namespace kanso
