@@ -100,6 +100,59 @@ __global__ void tc_pack_activations_kernel(const float* __restrict__ x,
   }
 }
 
+// The same pack with rmsnorm folded in (src/model.rs:653-659): one CTA per activation row
+// computes 1 / sqrt(mean(x^2) + eps), then packs x * r * norm_w. Rows >= M of the tile are
+// zeroed by the CTAs of rows M .. Mt-1.
+__global__ void tc_pack_norm_kernel(const float* __restrict__ x, const float* __restrict__ norm_w,
+                                    float eps, __half* __restrict__ xp, int M, int Mt, int K) {
+  __shared__ float s_red[32];
+  const int m = blockIdx.x;
+  float r = 0.f;
+  if (m < M) {
+    const float4* row = reinterpret_cast<const float4*>(x + (int64_t)m * K);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+      const float4 t = row[i];
+      ss += (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = threadIdx.x < (blockDim.x >> 5) ? s_red[threadIdx.x] : 0.f;
+    if (threadIdx.x < 32) {
+#pragma unroll
+      for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+      if (threadIdx.x == 0) s_red[0] = 1.0f / sqrtf(t / (float)K + eps);
+    }
+    __syncthreads();
+    r = s_red[0];
+  }
+  for (int chunk = threadIdx.x; chunk < K / 8; chunk += blockDim.x) {
+    __align__(16) __half hi[8], lo[8];
+    if (m < M) {
+      const float4* src = reinterpret_cast<const float4*>(x + (int64_t)m * K + chunk * 8);
+      const float4* nw = reinterpret_cast<const float4*>(norm_w + chunk * 8);
+      const float4 a = src[0], b = src[1], c = __ldg(nw), d = __ldg(nw + 1);
+      const float f[8] = {a.x * r * c.x, a.y * r * c.y, a.z * r * c.z, a.w * r * c.w,
+                          b.x * r * d.x, b.y * r * d.y, b.z * r * d.z, b.w * r * d.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        hi[j] = __float2half_rn(f[j]);
+        lo[j] = __float2half_rn(f[j] - __half2float(hi[j]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hi[j] = lo[j] = __float2half_rn(0.f);
+    }
+    const int stage = chunk >> 3, c8 = chunk & 7;
+    __half* base = xp + (int64_t)stage * (2 * 8 * Mt * 8);
+    *reinterpret_cast<uint4*>(base + ((int64_t)c8 * Mt + m) * 8) = *reinterpret_cast<uint4*>(hi);
+    *reinterpret_cast<uint4*>(base + ((int64_t)(8 + c8) * Mt + m) * 8) =
+        *reinterpret_cast<uint4*>(lo);
+  }
+}
+
 // ---- tcgen05 wrappers ----
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -506,16 +559,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
 // y_i[M,N_i] = x[M,K] @ W_i^T on the tensor cores for up to three matrices that share x, M up
 // to 128 per call (larger M is chunked by the caller). Optional fusions of the decode step:
-// x2 (activations are silu(x) * x2) and resid (y = resid + W.x, one matrix; may alias y).
+// x2 (activations are silu(x) * x2), norm_w (activations are rmsnorm(x) * norm_w) and resid
+// (y = resid + W.x, one matrix; may alias y).
 // Sets *handled = false (and launches nothing) when the shape is outside this kernel's range.
 int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void* const* w,
                         float* const* y, const int64_t* rows, const float* x, const float* x2,
-                        const float* resid, int64_t M, int64_t K, bool* handled) {
+                        const float* norm_w, float eps, const float* resid, int64_t M, int64_t K,
+                        bool* handled) {
   *handled = false;
   const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
   if (nseg < 1 || nseg > TC_MAX_SEGS || (resid && nseg != 1)) return KANSO_OK;
   if (M < 1 || M > 128 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
-  if (!aligned16(x) || (x2 && !aligned16(x2))) return KANSO_OK;
+  if (!aligned16(x) || (x2 && !aligned16(x2)) || (norm_w && (!aligned16(norm_w) || x2)))
+    return KANSO_OK;
   int tiles_n = 0;
   TcArgs a;
   for (int i = 0; i < nseg; ++i) {
@@ -548,8 +604,13 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
   *handled = true;
 
   const int64_t chunks = (K / 8) * Mt;
-  tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
-      x, x2, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
+  if (norm_w)
+    tc_pack_norm_kernel<<<Mt, 256, 0, ctx->stream>>>(x, norm_w, eps,
+                                                     reinterpret_cast<__half*>(scratch), (int)M,
+                                                     Mt, (int)K);
+  else
+    tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
+        x, x2, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
   int32_t st = after_launch(ctx, "gemm_tc pack activations");
   if (st) return st;
   a.resid = resid;
@@ -606,7 +667,8 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   const void* w1[1] = {w};
   float* y1[1] = {y};
   const int64_t r1[1] = {N};
-  return tc_matmul_multi(ctx, dtype, 1, w1, y1, r1, x, nullptr, nullptr, M, K, handled);
+  return tc_matmul_multi(ctx, dtype, 1, w1, y1, r1, x, nullptr, nullptr, 0.f, nullptr, M, K,
+                         handled);
 }
 
 }  // namespace kanso

@@ -14,7 +14,8 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
                                uint32_t max_ctx_hint, const PaDecodeFusion* fusion);
 int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void* const* w,
                         float* const* y, const int64_t* rows, const float* x, const float* x2,
-                        const float* resid, int64_t M, int64_t K, bool* handled);
+                        const float* norm_w, float eps, const float* resid, int64_t M, int64_t K,
+                        bool* handled);
 
 // Embedding rows of a Q8_0 table (src/weights.rs:50-57), bit-exact d * (f32)q.
 __global__ void model_embed_kernel(const uint8_t* __restrict__ w, const uint32_t* __restrict__ ids,
@@ -114,12 +115,12 @@ static int32_t ensure_ws(kanso_cuda_model* m, uint32_t B, uint32_t max_blocks) {
 }
 
 // Up to three projections of the same activations in one tensor-core GEMM launch (9..128
-// activation rows), with the SwiGLU product folded into the activation pack (x2) and the
-// residual add into the epilogue (resid). *handled = false, nothing launched, when the
+// activation rows), with rmsnorm (norm_w) or the SwiGLU product (x2) folded into the activation
+// pack and the residual add into the epilogue (resid). *handled = false, nothing launched, when the
 // weights or shapes are outside that kernel's range: the caller then runs the pieces singly.
 static int32_t lin_multi(kanso_cuda_ctx* ctx, int n, const ModelLin* const* l, float* const* y,
-                         const float* x, const float* x2, const float* resid, int64_t M,
-                         int32_t act_mode, bool* handled) {
+                         const float* x, const float* x2, const float* norm_w, float eps,
+                         const float* resid, int64_t M, int32_t act_mode, bool* handled) {
   *handled = false;
   if (act_mode != KANSO_ACT_F32 || M <= 8 || M > 128) return KANSO_OK;
   const void* w[3];
@@ -130,7 +131,8 @@ static int32_t lin_multi(kanso_cuda_ctx* ctx, int n, const ModelLin* const* l, f
     rows[i] = l[i]->rows;
   }
   if (l[0]->dtype != KANSO_DTYPE_Q8_0 && l[0]->dtype != KANSO_DTYPE_Q4_K) return KANSO_OK;
-  return tc_matmul_multi(ctx, l[0]->dtype, n, w, y, rows, x, x2, resid, M, l[0]->cols, handled);
+  return tc_matmul_multi(ctx, l[0]->dtype, n, w, y, rows, x, x2, norm_w, eps, resid, M,
+                         l[0]->cols, handled);
 }
 
 static int32_t lin(kanso_cuda_ctx* ctx, const ModelLin& l, const float* x, float* y, int64_t M,
@@ -369,16 +371,18 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
     auto& ly = m->layers[l];
     if (!ly.attn_norm || !ly.ffn_norm)
       return fail(ctx, KANSO_ERR_CONFIG, "decode_step: norm weights of layer %u not set", l);
-    if ((st = launch_rmsnorm(ctx, m->hidden, ly.attn_norm, m->normed, B, hidden, c.rms_norm_eps)))
-      return st;
     bool one = false;  // the launch below covered the whole group
     {
       const ModelLin* l3[3] = {&ly.w[KANSO_W_ATTN_Q], &ly.w[KANSO_W_ATTN_K], &ly.w[KANSO_W_ATTN_V]};
       float* y3[3] = {q, k, v};
-      if ((st = lin_multi(ctx, 3, l3, y3, m->normed, nullptr, nullptr, B, act_mode, &one)))
+      if ((st = lin_multi(ctx, 3, l3, y3, m->hidden, nullptr, ly.attn_norm, c.rms_norm_eps,
+                          nullptr, B, act_mode, &one)))
         return st;
     }
     if (!one) {
+      if ((st = launch_rmsnorm(ctx, m->hidden, ly.attn_norm, m->normed, B, hidden,
+                               c.rms_norm_eps)))
+        return st;
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_Q], m->normed, q, B, act_mode))) return st;
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_K], m->normed, k, B, act_mode))) return st;
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_V], m->normed, v, B, act_mode))) return st;
@@ -389,29 +393,32 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
     {
       const ModelLin* l1[1] = {&ly.w[KANSO_W_ATTN_OUTPUT]};
       float* y1[1] = {m->hidden};
-      if ((st = lin_multi(ctx, 1, l1, y1, m->attn, nullptr, m->hidden, B, act_mode, &one)))
+      if ((st = lin_multi(ctx, 1, l1, y1, m->attn, nullptr, nullptr, 0.f, m->hidden, B, act_mode,
+                          &one)))
         return st;
     }
     if (!one) {
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_OUTPUT], m->attn, m->proj, B, act_mode))) return st;
       if ((st = launch_residual_add(ctx, m->hidden, m->proj, (int64_t)B * hidden))) return st;
     }
-    if ((st = launch_rmsnorm(ctx, m->hidden, ly.ffn_norm, m->normed, B, hidden, c.rms_norm_eps)))
-      return st;
     {
       const ModelLin* l2[2] = {&ly.w[KANSO_W_FFN_GATE], &ly.w[KANSO_W_FFN_UP]};
       float* y2[2] = {m->gate, m->up};
-      if ((st = lin_multi(ctx, 2, l2, y2, m->normed, nullptr, nullptr, B, act_mode, &one)))
+      if ((st = lin_multi(ctx, 2, l2, y2, m->hidden, nullptr, ly.ffn_norm, c.rms_norm_eps, nullptr,
+                          B, act_mode, &one)))
         return st;
     }
     if (!one) {
+      if ((st = launch_rmsnorm(ctx, m->hidden, ly.ffn_norm, m->normed, B, hidden, c.rms_norm_eps)))
+        return st;
       if ((st = lin(ctx, ly.w[KANSO_W_FFN_GATE], m->normed, m->gate, B, act_mode))) return st;
       if ((st = lin(ctx, ly.w[KANSO_W_FFN_UP], m->normed, m->up, B, act_mode))) return st;
     }
     {
       const ModelLin* l1[1] = {&ly.w[KANSO_W_FFN_DOWN]};
       float* y1[1] = {m->hidden};
-      if ((st = lin_multi(ctx, 1, l1, y1, m->gate, m->up, m->hidden, B, act_mode, &one)))
+      if ((st = lin_multi(ctx, 1, l1, y1, m->gate, m->up, nullptr, 0.f, m->hidden, B, act_mode,
+                          &one)))
         return st;
     }
     if (!one) {
@@ -419,6 +426,15 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
       if ((st = lin(ctx, ly.w[KANSO_W_FFN_DOWN], m->act, m->proj, B, act_mode))) return st;
       if ((st = launch_residual_add(ctx, m->hidden, m->proj, (int64_t)B * hidden))) return st;
     }
+  }
+  {
+    bool one = false;
+    const ModelLin* l1[1] = {&head};
+    float* y1[1] = {logits_dev};
+    if ((st = lin_multi(ctx, 1, l1, y1, m->hidden, nullptr, m->final_norm, c.rms_norm_eps, nullptr,
+                        B, act_mode, &one)) ||
+        one)
+      return st;
   }
   if ((st = launch_rmsnorm(ctx, m->hidden, m->final_norm, m->normed, B, hidden, c.rms_norm_eps)))
     return st;
