@@ -205,6 +205,13 @@ int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weig
                                       const float* x, int64_t M, float* const* y_out,
                                       int32_t n_out, int64_t n_total, int64_t row_offset,
                                       int32_t act_mode);
+/* K sharding with the reduction done through the same peer stores: every rank stores its
+ * partial y into slice [rank * rows, (rank + 1) * rows) of every rank's parts buffer
+ * (f32 [M, world * rows]) with kanso_cuda_linear_scatter_out(n_total = world * rows,
+ * row_offset = rank * rows); after the caller's cross-GPU barrier this adds the slices in rank
+ * order: y[m, n] = sum_r parts[m, r * rows + n]. No counterpart in the reference. */
+int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M, int64_t rows,
+                              int32_t world, float* y);
 /* LinearWeight::embed — src/weights.rs:50-57: dequantise the selected rows.
  * ids u32[T] (device), out f32[T, cols] (device). An id >= rows -> KANSO_ERR_SHAPE
  * is reported by the device status word at the next kanso_cuda_sync. */

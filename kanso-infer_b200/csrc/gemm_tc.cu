@@ -593,11 +593,15 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
   a.nseg = nseg;
   const int Mt = (int)((M + 15) / 16 * 16);
   const int stages_total = (int)(K / TC_KC);
-  // Split K only when the row tiles alone would leave more than half of the SMs idle: the
-  // partial sums of a split are added with atomics (onto the residual, or after a clear of
-  // y), which costs more than an under-filled grid does. At least 4 stages stay in every CTA.
+  // Split K while the grid stays within about one wave of CTAs (one CTA per SM): the decode
+  // step's matrices have 8 to 40 row tiles and would otherwise leave most SMs idle. Large
+  // matrices are not split: a second partial wave costs more than it gains, and the partial
+  // sums of a split are added with atomics (onto the residual, or after a clear of y). At
+  // least 2 stages stay in every CTA.
   int ksplit = 1;
-  while (tiles_n * ksplit * 2 <= ctx->sm_count && stages_total / (ksplit * 2) >= 4) ksplit *= 2;
+  while (tiles_n * ksplit * 2 <= ctx->sm_count + ctx->sm_count / 4 &&
+         stages_total / (ksplit * 2) >= 2)
+    ksplit *= 2;
   const size_t xp_bytes = 2 * (size_t)(K / 8) * Mt * 16;
   uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
   if (!scratch) return KANSO_ERR_DEVICE;

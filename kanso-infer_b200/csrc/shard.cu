@@ -34,6 +34,19 @@ __global__ void scatter_rows_kernel(const float* __restrict__ src, ScatterArgs a
 
 using namespace kanso;
 
+// y[m, n] = sum over r of parts[m, r * rows + n], added in rank order (every rank gets the same
+// bits).
+__global__ void sum_shards_kernel(const float* __restrict__ parts, int64_t M, int64_t rows,
+                                  int world, float* __restrict__ y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * rows) return;
+  const int64_t m = i / rows, n = i - m * rows;
+  const float* p = parts + m * rows * world + n;
+  float s = 0.f;
+  for (int r = 0; r < world; ++r) s += p[(int64_t)r * rows];
+  y[i] = s;
+}
+
 extern "C" {
 
 int32_t kanso_cuda_shard_range(int64_t n, int32_t rank, int32_t world, int64_t align,
@@ -110,6 +123,19 @@ int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weig
   scatter_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(tmp, sa, M, w->rows,
                                                                            n_total, row_offset);
   return after_launch(ctx, "linear_scatter_out");
+}
+
+int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M, int64_t rows,
+                              int32_t world, float* y) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "sum_shards: ctx is NULL");
+  if (!parts || !y) return fail(ctx, KANSO_ERR_SHAPE, "sum_shards: NULL pointer");
+  if (M < 0 || rows < 0 || world < 1 || world > 64)
+    return fail(ctx, KANSO_ERR_SHAPE, "sum_shards: bad shape (M %lld, rows %lld, world %d)",
+                (long long)M, (long long)rows, world);
+  const int64_t n = M * rows;
+  if (n == 0) return KANSO_OK;
+  sum_shards_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(parts, M, rows, world, y);
+  return after_launch(ctx, "sum_shards");
 }
 
 }  // extern "C"

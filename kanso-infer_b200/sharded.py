@@ -4,7 +4,11 @@ Row sharding (W_up): rank r holds a contiguous range of output rows; y is assemb
 an NCCL all-gather ("nccl") or by the matmul kernel itself storing its slice into every
 peer's result buffer over NVLink ("fused", symmetric memory + one cross-GPU barrier).
 K sharding (W_down): rank r holds the blocks of a contiguous range of columns, re-packed;
-partial results are summed with an NCCL all-reduce.
+partial results are summed with an NCCL all-reduce ("nccl") or exchanged by the matmul
+kernel's own peer stores and added locally in rank order ("fused").
+
+The fused modes alternate between two symmetric buffers: a rank that is one call ahead of a
+peer then never stores into the buffer that peer is still reading.
 
 This module holds no arithmetic: slicing of block bytes and calls into the C ABI.
 """
@@ -75,10 +79,14 @@ class RowShardedLinear:
         self.even = len(set(counts)) == 1
         if mode == "fused":
             import torch.distributed._symmetric_memory as symm
-            self.y_full = symm.empty((max_m, rows), dtype=torch.float32, device="cuda")
-            self.hdl = symm.rendezvous(self.y_full, self.group.group_name)
-            ptrs = [int(p) for p in self.hdl.buffer_ptrs]
-            self._ptrs = (C.c_void_p * self.world)(*ptrs)
+            self._bufs, self._hdls, self._ptrs, self._turn = [], [], [], 0
+            for _ in range(2):
+                buf = symm.empty((max_m, rows), dtype=torch.float32, device="cuda")
+                hdl = symm.rendezvous(buf, self.group.group_name)
+                self._bufs.append(buf)
+                self._hdls.append(hdl)
+                self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
+            self.y_full = self._bufs[0]
         elif mode == "nccl":
             self.y_full = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
             self.y_local = torch.empty((max_m, self.row_count), dtype=torch.float32, device="cuda")
@@ -92,10 +100,13 @@ class RowShardedLinear:
             raise kb.KansoError(kb.ERR_SHAPE, f"M {M} exceeds the buffers sized for {self.max_m}")
         if self.mode == "fused":
             # every rank stores its slice into every rank's y_full, then one barrier
+            t = self._turn
+            self._turn ^= 1
             self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x), M,
-                          C.cast(self._ptrs, C.c_void_p), self.world, self.rows, self.row_begin,
-                          act_mode)
-            self.hdl.barrier(channel=0)
+                          C.cast(self._ptrs[t], C.c_void_p), self.world, self.rows,
+                          self.row_begin, act_mode)
+            self._hdls[t].barrier(channel=0)
+            self.y_full = self._bufs[t]
             return self.y_full[:M]
         y_local = self.y_local[:M]
         self.weight.forward(x, y_local, M, act_mode)
@@ -117,12 +128,12 @@ class KShardedLinear:
     summed y on every rank (all-reduce)."""
 
     def __init__(self, ctx: kb.Context, blocks, dtype, rows, cols, group=None, max_m=8,
-                 presharded=False):
+                 presharded=False, mode="nccl"):
         """blocks: the whole block matrix, or with presharded=True this rank's re-packed
         [rows x cols/world] columns (cols is always the total)."""
         import torch
         import torch.distributed as dist
-        self.ctx, self.rows, self.cols = ctx, rows, cols
+        self.ctx, self.rows, self.cols, self.mode = ctx, rows, cols, mode
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         if presharded:
@@ -135,11 +146,36 @@ class KShardedLinear:
         self.weight = kb.Weight(ctx, shard, dtype, rows, self.col_count)
         self.y = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
         self.max_m = max_m
+        if mode == "fused":
+            if self.world > 8:
+                raise kb.KansoError(kb.ERR_UNSUPPORTED, "fused K sharding: at most 8 ranks")
+            import torch.distributed._symmetric_memory as symm
+            self._bufs, self._hdls, self._ptrs, self._turn = [], [], [], 0
+            for _ in range(2):
+                buf = symm.empty((max_m, self.world * rows), dtype=torch.float32, device="cuda")
+                hdl = symm.rendezvous(buf, self.group.group_name)
+                self._bufs.append(buf)
+                self._hdls.append(hdl)
+                self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
+        elif mode != "nccl":
+            raise ValueError(mode)
 
     def forward(self, x_slice, M=1, act_mode=kb.ACT_F32):
         """x_slice: device f32 [M, col_count] = columns [col_begin, col_begin + col_count) of x."""
         import torch.distributed as dist
         y = self.y[:M]
+        if self.mode == "fused":
+            # every rank stores its partial y into its slice of every rank's buffer; after
+            # one barrier each rank adds the slices itself, in rank order
+            t = self._turn
+            self._turn ^= 1
+            self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x_slice), M,
+                          C.cast(self._ptrs[t], C.c_void_p), self.world, self.world * self.rows,
+                          self.rank * self.rows, act_mode)
+            self._hdls[t].barrier(channel=0)
+            self.ctx.call("kanso_cuda_sum_shards", kb._ptr(self._bufs[t]), M, self.rows,
+                          self.world, kb._ptr(y))
+            return y
         self.weight.forward(x_slice, y, M, act_mode)
         dist.all_reduce(y, group=self.group)
         return y

@@ -57,12 +57,15 @@ def _worker(rank, world, port, q):
                     torch.cuda.synchronize()
                     assert rel(y.cpu().numpy(), ref) <= 1e-3, (mode, M)
                     dist.barrier()
-            klin = sh.KShardedLinear(ctx, blocks, kb.DTYPE_Q4_K, rows, cols)
-            xs = xd[:, klin.col_begin:klin.col_begin + klin.col_count].contiguous()
-            y = klin.forward(xs, M)
-            ctx.sync()
-            torch.cuda.synchronize()
-            assert rel(y.cpu().numpy(), ref) <= 1e-3, ("k", M)
+            for mode in ("nccl", "fused"):
+                klin = sh.KShardedLinear(ctx, blocks, kb.DTYPE_Q4_K, rows, cols, mode=mode)
+                xs = xd[:, klin.col_begin:klin.col_begin + klin.col_count].contiguous()
+                for _ in range(3):
+                    y = klin.forward(xs, M)
+                    ctx.sync()
+                    torch.cuda.synchronize()
+                    assert rel(y.cpu().numpy(), ref) <= 1e-3, ("k", mode, M)
+                    dist.barrier()
         # Q8_0 takes the general path (slice to scratch, then a scatter kernel)
         b8 = O.quantize_weights_q8_0(w[:512])
         x = rng.standard_normal((1, cols)).astype(np.float32)
