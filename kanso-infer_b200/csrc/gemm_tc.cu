@@ -37,12 +37,11 @@ namespace kanso {
 
 constexpr int TC_PRODUCERS = 512;           // threads that copy, dequantise and run the epilogue
 constexpr int TC_THREADS = TC_PRODUCERS + 32;  // plus one warp that issues the MMAs
+constexpr int TC_MAX_SEGS = 3;   // matrices of one launch that share the activations (Q, K, V)
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
 constexpr int TC_A_PLANE = TC_TILE_N * TC_KC * 2;  // bytes of one f16 A term per stage (16 KB)
 constexpr int TC_A_STAGE = 2 * TC_A_PLANE;         // hi and lo terms
-
-constexpr int TC_MAX_SEGS = 3;  // matrices of one launch that share the activations (Q, K, V)
 
 struct TcArgs {
   const uint8_t* w[TC_MAX_SEGS];
@@ -61,11 +60,27 @@ struct TcArgs {
 };
 
 
+// Result buffers the pack kernels clear on the way (a split-K GEMM adds into them).
+struct TcZero {
+  float* p[TC_MAX_SEGS];
+  int64_t n[TC_MAX_SEGS];
+};
+__device__ __forceinline__ void tc_zero_fill(const TcZero& z, int64_t tid, int64_t nthreads) {
+#pragma unroll
+  for (int i = 0; i < TC_MAX_SEGS; ++i)
+    for (int64_t j = tid; j < z.n[i]; j += nthreads) z.p[i][j] = 0.f;
+}
+
 // x f32 [M,K] -> two f16 terms xh + xl, layout [stage][term][chunk of 8 k][row m][8 values];
 // rows >= M are zero.
 __global__ void tc_pack_activations_kernel(const float* __restrict__ x,
                                            const float* __restrict__ x2,
-                                           __half* __restrict__ xp, int M, int Mt, int K) {
+                                           __half* __restrict__ xp, int M, int Mt, int K,
+                                           const TcZero zero) {
+  pdl_launch_dependents();
+  pdl_wait();  // x (and the readers of the buffers cleared here) belong to earlier kernels
+  tc_zero_fill(zero, (int64_t)blockIdx.x * blockDim.x + threadIdx.x,
+               (int64_t)gridDim.x * blockDim.x);
   const int64_t total = (int64_t)(K / 8) * Mt;  // one thread per (chunk, row)
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -104,8 +119,13 @@ __global__ void tc_pack_activations_kernel(const float* __restrict__ x,
 // computes 1 / sqrt(mean(x^2) + eps), then packs x * r * norm_w. Rows >= M of the tile are
 // zeroed by the CTAs of rows M .. Mt-1.
 __global__ void tc_pack_norm_kernel(const float* __restrict__ x, const float* __restrict__ norm_w,
-                                    float eps, __half* __restrict__ xp, int M, int Mt, int K) {
+                                    float eps, __half* __restrict__ xp, int M, int Mt, int K,
+                                    const TcZero zero) {
   __shared__ float s_red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  tc_zero_fill(zero, (int64_t)blockIdx.x * blockDim.x + threadIdx.x,
+               (int64_t)gridDim.x * blockDim.x);
   const int m = blockIdx.x;
   float r = 0.f;
   if (m < M) {
@@ -424,6 +444,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Dependent launch: the weights never depend on the kernel before this one (the activation
+  // pack), so the producers start fetching them at once; the MMA warp waits for the pack
+  // before it touches the packed activations, and every store to y comes after MMAs that
+  // consumed them.
+  pdl_launch_dependents();
 
   if (warp < TC_PRODUCERS / 32) {
     TcRawCopy<FMT> raw_copy;
@@ -475,6 +500,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         mbar_arrive_expect_tx(&bfull[b], b_stage);
         bulk_g2s(Bs + b * b_stage, bsrc + (size_t)s * b_stage, b_stage, &bfull[b]);
       };
+      pdl_wait();
       for (int i = 0; i < NS - 1 && s0 + i < s1; ++i) copy_b(s0 + i, i);
       int buf = 0, prev = NS - 1;  // prev = buffer of stage s - 1 = buffer of stage s + NS - 1
       uint32_t par = 0, prev_par = 1;
@@ -607,33 +633,37 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
   if (!scratch) return KANSO_ERR_DEVICE;
   *handled = true;
 
-  const int64_t chunks = (K / 8) * Mt;
-  if (norm_w)
-    tc_pack_norm_kernel<<<Mt, 256, 0, ctx->stream>>>(x, norm_w, eps,
-                                                     reinterpret_cast<__half*>(scratch), (int)M,
-                                                     Mt, (int)K);
-  else
-    tc_pack_activations_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>(
-        x, x2, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K);
-  int32_t st = after_launch(ctx, "gemm_tc pack activations");
-  if (st) return st;
   a.resid = resid;
+  TcZero zero = {};
   if (ksplit > 1) {
-    // the K slices add into y: y must hold the residual (in place) or zeros
+    // the K slices add into y: y must hold the residual (in place) or zeros (cleared by the
+    // pack kernel below)
     a.resid = nullptr;
     for (int i = 0; i < nseg; ++i) {
       if (resid && resid == y[i]) continue;
-      if (resid)
+      if (resid) {
         KANSO_CUDA_TRY(ctx,
                        cudaMemcpyAsync(y[i], resid, sizeof(float) * (size_t)M * rows[i],
                                        cudaMemcpyDeviceToDevice, ctx->stream),
                        "gemm_tc: residual copy");
-      else
-        KANSO_CUDA_TRY(ctx,
-                       cudaMemsetAsync(y[i], 0, sizeof(float) * (size_t)M * rows[i], ctx->stream),
-                       "gemm_tc: clear y");
+      } else {
+        zero.p[i] = y[i];
+        zero.n[i] = M * rows[i];
+      }
     }
   }
+  const int64_t chunks = (K / 8) * Mt;
+  cudaError_t le;
+  if (norm_w)
+    le = launch_dependent(ctx, tc_pack_norm_kernel, dim3(Mt), dim3(256), 0, x, norm_w, eps,
+                          reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, zero);
+  else
+    le = launch_dependent(ctx, tc_pack_activations_kernel,
+                          dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, x, x2,
+                          reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, zero);
+  if (le != cudaSuccess) return cuda_fail(ctx, le, "gemm_tc pack launch");
+  int32_t st = after_launch(ctx, "gemm_tc pack activations");
+  if (st) return st;
   a.xp = reinterpret_cast<const __half*>(scratch);
   a.K = (int)K;
   a.M = (int)M;
@@ -662,7 +692,8 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
                    "gemm_tc: shared memory opt-in");
     done = true;
   }
-  kern<<<dim3(tiles_n, ksplit), TC_THREADS, smem, ctx->stream>>>(a);
+  le = launch_dependent(ctx, kern, dim3(tiles_n, ksplit), dim3(TC_THREADS), smem, a);
+  if (le != cudaSuccess) return cuda_fail(ctx, le, "gemm_tc launch");
   return after_launch(ctx, "gemm_tc");
 }
 
