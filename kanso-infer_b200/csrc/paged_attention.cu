@@ -24,6 +24,8 @@
 namespace kanso {
 
 constexpr int PA_THREADS = 128;
+constexpr int PA_BIG_THREADS = 256;  // partitions of 256 tokens and more
+__host__ inline uint32_t pa_threads(uint32_t pt) { return pt >= 256 ? PA_BIG_THREADS : PA_THREADS; }
 constexpr int PA_MAX_GROUP = 8;      // MAX_KV_GROUP_SIZE, src/metal/paged_attention.rs:10
 constexpr int PA_MAX_HEAD_DIM = 256; // MAX_HEAD_DIM, src/metal/paged_attention.rs:8
 
@@ -62,13 +64,14 @@ __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
 // NT = threads per CTA.
 template <int G, int NT>
 __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
   const uint32_t hd = a.g.head_dim, bs = a.g.block_size;
   const uint32_t part = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   // Inside the decode step (fused mode) the context lengths, positions, slots and the block
-  // table are inputs of the whole step, written before its first kernel: they are read before
-  // the wait, and only q and the new K/V rows, which the previous kernel produces, after it.
+  // table are inputs of the whole step, written before its first kernel, and the cache rows of
+  // earlier steps do not depend on the kernel before this one either: all of them are read
+  // before the wait, and only q and the new K/V rows, which that kernel produces, after it.
   const bool fused = a.k_new != nullptr;
   uint32_t ctx = 0, pos = 0;
   if (fused) {
@@ -88,28 +91,32 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   if (t0 >= ctx) return;
   const uint32_t n = min(a.part_tokens, ctx - t0);
   const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
 
-  // shared: q planes, q scales, block ids, probabilities, reduction scratch
-  int8_t* qhi = reinterpret_cast<int8_t*>(smem);            // [G][hd]
+  // shared: the partition's block records (K, V and their scales, as they lie in the pool),
+  // mbarrier, q planes, q scales, block ids, probabilities, reduction scratch
+  const uint32_t max_blk = (a.part_tokens + bs - 1) / bs;
+  uint8_t* tiles = smem;                                                    // 16-byte records
+  uint64_t* bar = reinterpret_cast<uint64_t*>(tiles + (size_t)max_blk * a.g.rec_bytes);
+  int8_t* qhi = reinterpret_cast<int8_t*>(bar + 2);          // [G][hd]
   int8_t* qlo = qhi + G * hd;                                // [G][hd]
   float* qd = reinterpret_cast<float*>(qlo + G * hd);        // [G] (d/254)
   uint32_t* blk = reinterpret_cast<uint32_t*>(qd + PA_MAX_GROUP);  // [part_tokens/bs + 1]
-  const uint32_t nblk_part = ((a.part_tokens + bs - 1) / bs + 4) & ~3u;
+  const uint32_t nblk_part = (max_blk + 4) & ~3u;
   float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
-  float* vscs = prob + ((G * a.part_tokens + 3) & ~3u);      // [part_tokens] V scales
-  float* red = vscs + ((a.part_tokens + 3) & ~3u);           // PV scratch, 16-byte aligned
+  float* red = prob + ((G * a.part_tokens + 3) & ~3u);       // PV scratch, 16-byte aligned
 
-  // physical blocks of this partition (bounds-checked once)
+  // physical blocks of this partition (bounds-checked once); partitions start on a block
+  const uint32_t nb = (n + bs - 1) / bs;
   {
     const uint32_t first_blk = t0 / bs;
-    const uint32_t last_blk = (t0 + n - 1) / bs;
-    for (uint32_t b = first_blk + tid; b <= last_blk; b += NT) {
-      uint32_t phys = a.tables[(size_t)seq * a.max_blocks + b];
+    for (uint32_t b = tid; b < nb; b += NT) {
+      uint32_t phys = a.tables[(size_t)seq * a.max_blocks + first_blk + b];
       if (phys >= a.g.num_blocks) {
         atomicOr(a.status, DEV_BAD_INDEX);
         phys = 0;
       }
-      blk[b - first_blk] = phys;
+      blk[b] = phys;
     }
   }
   // RoPE factors of this sequence's position, and the pool slot of its newest token
@@ -126,215 +133,150 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     }
     new_slot = a.slots[seq];
   }
-  __syncthreads();  // block ids and RoPE factors are in shared memory
-  const uint32_t first_blk = t0 / bs;
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();  // block ids, RoPE factors and the barrier are in shared memory
+
+  // One bulk copy per block record brings K, V and both scale rows of 16 tokens (2176 bytes at
+  // head_dim 64) into shared memory; the whole partition is in flight at once.
+  if (warp == 0) {
+    if (lane == 0) mbar_arrive_expect_tx(bar, nb * a.g.rec_bytes);
+    __syncwarp();
+    for (uint32_t b = lane; b < nb; b += 32)
+      bulk_g2s(tiles + (size_t)b * a.g.rec_bytes,
+               a.g.pool + a.g.rec_offset(a.layer, blk[b], kvh), a.g.rec_bytes, bar);
+  }
   // position of the newest token inside this partition (fused mode), else out of range
   const uint32_t i_new = (fused && ctx - 1 >= t0 && ctx - 1 < t0 + n) ? ctx - 1 - t0 : 0xFFFFFFFFu;
-  __shared__ __align__(16) int8_t s_newk[PA_MAX_HEAD_DIM], s_newv[PA_MAX_HEAD_DIM];
-  __shared__ float s_newsc[2];
-
-  // The cache rows of earlier steps do not depend on the kernel before this one either: the
-  // first K row of every thread, its scales, and the first four V words of every thread are
-  // requested here, before the wait.
-  // PV tiling: thread = (8 dims = one 64-bit word c of the V row, token slice); later groups of
-  // four tokens are loaded one group ahead of their use.
-  const uint32_t dwords = hd / 8;
-  const uint32_t nslice = NT / dwords;  // hd in {16..256} -> dwords in {2..32}
-  const uint32_t c = tid % dwords, slice = tid / dwords;
-  auto load_v = [&](uint32_t i0, uint2 (&vw)[4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t i = i0 + j * nslice;
-      if (i < n) {
-        const uint32_t t = t0 + i;
-        const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-        const uint2* vp =
-            reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(t % bs) * hd) + c;
-        if (i == i_new)
-          vw[j] = reinterpret_cast<const uint2*>(s_newv)[c];  // stored by this CTA a moment ago
-        else
-          vw[j] = __ldg(vp);
-      } else {
-        vw[j] = make_uint2(0u, 0u);
-      }
-    }
-  };
-  uint2 vcur[4];
-  load_v(slice, vcur);
-  const uint32_t nchunk = hd / 16;
-  uint4 kpre[4];
-  float kscp = 0.f, vscp = 0.f;
-  if ((uint32_t)tid < n) {
-    const uint32_t t = t0 + tid;
-    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-    const uint32_t off = t % bs;
-    const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      kpre[j] = (uint32_t)j < nchunk ? __ldg(krow + j) : make_uint4(0, 0, 0, 0);
-    kscp = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
-    vscp = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
-  }
   if (fused) pdl_wait();  // q and the new K/V rows come from the kernel before this one
 
   // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
-  {
-    const int warp = tid >> 5, lane = tid & 31;
-    const uint32_t half = hd / 2;
-    const float* cs = s_cos;
-    const float* sn = s_sin;
-    // element d of a head after rotate-half RoPE; multiplies and adds round separately, as
-    // the reference's tensor ops do (the stored K bytes must equal the CPU path's)
-    auto roped = [&](const float* row, uint32_t d) {
-      if (!fused) return row[d];
-      const uint32_t j = d < half ? d : d - half;
-      const float x0 = row[j], x1 = row[j + half], c_ = cs[j], s_ = sn[j];
-      return d < half ? __fsub_rn(__fmul_rn(x0, c_), __fmul_rn(x1, s_))
-                      : __fadd_rn(__fmul_rn(x0, s_), __fmul_rn(x1, c_));
-    };
-    for (int gq = warp; gq < G; gq += NT / 32) {
-      const float* qrow = a.q + ((size_t)seq * a.num_heads + (size_t)kvh * G + gq) * hd;
-      constexpr int QE = PA_MAX_HEAD_DIM / 32;
-      float qe[QE];  // this lane's elements of the head, loaded (and rotated) once
-      float amax = 0.f;
+  constexpr int QE = PA_MAX_HEAD_DIM / 32;
+  const uint32_t half = hd / 2;
+  // element d of a head after rotate-half RoPE; multiplies and adds round separately, as
+  // the reference's tensor ops do (the stored K bytes must equal the CPU path's)
+  auto roped = [&](const float* row, uint32_t d) {
+    if (!fused) return row[d];
+    const uint32_t j = d < half ? d : d - half;
+    const float x0 = row[j], x1 = row[j + half], c_ = s_cos[j], s_ = s_sin[j];
+    return d < half ? __fsub_rn(__fmul_rn(x0, c_), __fmul_rn(x1, s_))
+                    : __fadd_rn(__fmul_rn(x0, s_), __fmul_rn(x1, c_));
+  };
+  // the newest token's K (warp 0) and V (warp 1): rotated and quantised in registers first
+  // (quantize_head_slice, src/kv_cache/quantized_storage.rs:452-469), stored once the copies
+  // above have landed
+  const bool writer = i_new != 0xFFFFFFFFu && warp < 2;
+  float ne[QE];
+  float new_scale = 1.0f, new_inv = 1.0f;
+  if (writer) {
+    const bool is_k = warp == 0;
+    const float* src = (is_k ? a.k_new : a.v_new) + ((size_t)seq * a.g.kv_heads + kvh) * hd;
+    float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < QE; ++i) {
-        const uint32_t d = lane + 32 * i;
-        qe[i] = d < hd ? roped(qrow, d) : 0.f;
-        amax = fmaxf(amax, fabsf(qe[i]));
+    for (int i = 0; i < QE; ++i) {
+      const uint32_t d = lane + 32 * i;
+      ne[i] = 0.f;
+      if (d < hd) {
+        ne[i] = is_k ? roped(src, d) : src[d];
+        amax = fmaxf(amax, fabsf(ne[i]));
       }
+    }
 #pragma unroll
-      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-      float d_ = amax / 127.0f;
-      float id = d_ != 0.f ? 1.0f / d_ : 0.f;
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    new_scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    new_inv = __fdiv_rn(1.0f, new_scale);
+  }
+  for (int gq = warp; gq < G; gq += NT / 32) {
+    const float* qrow = a.q + ((size_t)seq * a.num_heads + (size_t)kvh * G + gq) * hd;
+    float qe[QE];  // this lane's elements of the head, loaded (and rotated) once
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < QE; ++i) {
+      const uint32_t d = lane + 32 * i;
+      qe[i] = d < hd ? roped(qrow, d) : 0.f;
+      amax = fmaxf(amax, fabsf(qe[i]));
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    float d_ = amax / 127.0f;
+    float id = d_ != 0.f ? 1.0f / d_ : 0.f;
+#pragma unroll
+    for (int i = 0; i < QE; ++i) {
+      const uint32_t d = lane + 32 * i;
+      if (d < hd) {
+        float x = qe[i];
+        float h = fminf(fmaxf(rintf(x * id), -127.f), 127.f);
+        float l = fminf(fmaxf(rintf(fmaf(-d_, h, x) * (254.0f * id)), -127.f), 127.f);
+        qhi[gq * hd + d] = (int8_t)h;
+        qlo[gq * hd + d] = (int8_t)l;
+      }
+    }
+    if (lane == 0) qd[gq] = d_ * (1.0f / 254.0f);
+  }
+  // the partition's records are in shared memory from here on (bounded wait: a copy that
+  // never lands is reported through the status word, the CTA carries on with what it has)
+  if (!mbar_wait_bounded(bar, 0) && tid == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
+  if (writer) {
+    const bool is_k = warp == 0;
+    const uint32_t block = new_slot / bs, off = new_slot % bs;
+    if (block >= a.g.num_blocks) {
+      if (lane == 0) atomicOr(a.status, DEV_BAD_INDEX);
+    } else {
+      uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, block, kvh);
+      uint8_t* tile = tiles + (size_t)(i_new / bs) * a.g.rec_bytes;  // this CTA's own copy
+      const uint32_t row = (is_k ? a.g.k_off() : a.g.v_off());
+      int8_t* dst = reinterpret_cast<int8_t*>(rec + row) + (size_t)off * hd;
+      int8_t* mine = reinterpret_cast<int8_t*>(tile + row) + (size_t)(i_new % bs) * hd;
 #pragma unroll
       for (int i = 0; i < QE; ++i) {
         const uint32_t d = lane + 32 * i;
         if (d < hd) {
-          float x = qe[i];
-          float h = fminf(fmaxf(rintf(x * id), -127.f), 127.f);
-          float l = fminf(fmaxf(rintf(fmaf(-d_, h, x) * (254.0f * id)), -127.f), 127.f);
-          qhi[gq * hd + d] = (int8_t)h;
-          qlo[gq * hd + d] = (int8_t)l;
+          const int8_t qv = (int8_t)fminf(fmaxf(roundf(__fmul_rn(ne[i], new_inv)), -127.f), 127.f);
+          dst[d] = qv;
+          mine[d] = qv;
         }
       }
-      if (lane == 0) qd[gq] = d_ * (1.0f / 254.0f);
-    }
-    // the newest token's K (warp 0) and V (warp 1) into the pool, by the CTA that reads them
-    // (quantize_head_slice, src/kv_cache/quantized_storage.rs:452-469)
-    if (fused && warp < 2 && ctx - 1 >= t0 && ctx - 1 < t0 + n) {
-      const bool is_k = warp == 0;
-      const float* src = (is_k ? a.k_new : a.v_new) + ((size_t)seq * a.g.kv_heads + kvh) * hd;
-      const uint32_t sl = new_slot;
-      const uint32_t block = sl / bs, off = sl % bs;
-      if (block >= a.g.num_blocks) {
-        if (lane == 0) atomicOr(a.status, DEV_BAD_INDEX);
-      } else {
-        constexpr int MAXE = PA_MAX_HEAD_DIM / 32;
-        float e[MAXE];
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXE; ++i) {
-          const uint32_t d = lane + 32 * i;
-          e[i] = 0.f;
-          if (d < hd) {
-            e[i] = is_k ? roped(src, d) : src[d];
-            amax = fmaxf(amax, fabsf(e[i]));
-          }
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-        const float inv = __fdiv_rn(1.0f, scale);
-        uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, block, kvh);
-        int8_t* dst =
-            reinterpret_cast<int8_t*>(rec + (is_k ? a.g.k_off() : a.g.v_off())) + (size_t)off * hd;
-        int8_t* mine = is_k ? s_newk : s_newv;  // this CTA reads the row back from here
-#pragma unroll
-        for (int i = 0; i < MAXE; ++i) {
-          const uint32_t d = lane + 32 * i;
-          if (d < hd) {
-            const int8_t qv = (int8_t)fminf(fmaxf(roundf(__fmul_rn(e[i], inv)), -127.f), 127.f);
-            dst[d] = qv;
-            mine[d] = qv;
-          }
-        }
-        if (lane == 0) {
-          reinterpret_cast<float*>(rec + (is_k ? a.g.ks_off() : a.g.vs_off()))[off] = scale;
-          s_newsc[is_k ? 0 : 1] = scale;
-        }
+      if (lane == 0) {
+        const uint32_t so = is_k ? a.g.ks_off() : a.g.vs_off();
+        reinterpret_cast<float*>(rec + so)[off] = new_scale;
+        reinterpret_cast<float*>(tile + so)[i_new % bs] = new_scale;
       }
     }
   }
   __syncthreads();
-  // the newest token's row was requested before it existed: take it from shared memory
-  if (i_new != 0xFFFFFFFFu) {
-    if ((uint32_t)tid == i_new) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if ((uint32_t)j < nchunk) kpre[j] = reinterpret_cast<const uint4*>(s_newk)[j];
-      kscp = s_newsc[0];
-      vscp = s_newsc[1];
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (slice + j * nslice == i_new) vcur[j] = reinterpret_cast<const uint2*>(s_newv)[c];
-  }
 
-  // --- QK: one thread per token
+  // --- QK: one thread per token, rows read from the staged records. Lanes start at different
+  // 16-byte chunks of their rows (rows are 64 bytes apart at head_dim 64: without the rotation
+  // eight lanes would share two banks).
+  const uint32_t nchunk = hd / 16;
   float lmax[G];
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) lmax[gq] = -INFINITY;
   for (uint32_t i = tid; i < n; i += NT) {
-    const uint32_t t = t0 + i;
-    const uint8_t* rec = a.g.pool + a.g.rec_offset(a.layer, blk[t / bs - first_blk], kvh);
-    const uint32_t off = t % bs;
-    const bool first = i == (uint32_t)tid;  // this thread's first token: row already here
+    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
+    const uint32_t off = i % bs;
     const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
-    const uint4* knew = reinterpret_cast<const uint4*>(s_newk);
-    float ksc, vsc_i;
-    if (first) {
-      ksc = kscp;
-      vsc_i = vscp;
-    } else if (i == i_new) {
-      ksc = s_newsc[0];
-      vsc_i = s_newsc[1];
-    } else {
-      ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
-      vsc_i = reinterpret_cast<const float*>(rec + a.g.vs_off())[off];
-    }
-    vscs[i] = vsc_i;
+    const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
     int ih[G], il[G];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) ih[gq] = il[gq] = 0;
-    for (uint32_t c0 = 0; c0 < nchunk; c0 += 4) {
-      uint4 kw4[4];  // four chunks of the row in flight (head_dim 16 and 32 have fewer)
+    for (uint32_t cc = 0; cc < nchunk; ++cc) {
+      const uint32_t c = (cc + (i >> 1)) & (nchunk - 1);
+      const uint4 kw = krow[c];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (first && c0 == 0)
-          kw4[j] = kpre[j];
-        else
-          kw4[j] = c0 + j < nchunk ? (i == i_new ? knew[c0 + j] : __ldg(krow + c0 + j))
-                                   : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (c0 + j >= nchunk) break;
-        const uint4 kw = kw4[j];
-        const uint32_t c = c0 + j;
-#pragma unroll
-        for (int gq = 0; gq < G; ++gq) {
-          const uint4 h4 = *reinterpret_cast<const uint4*>(qhi + gq * hd + 16 * c);
-          const uint4 l4 = *reinterpret_cast<const uint4*>(qlo + gq * hd + 16 * c);
-          ih[gq] = dp4a_ss((int)kw.x, (int)h4.x, ih[gq]);
-          ih[gq] = dp4a_ss((int)kw.y, (int)h4.y, ih[gq]);
-          ih[gq] = dp4a_ss((int)kw.z, (int)h4.z, ih[gq]);
-          ih[gq] = dp4a_ss((int)kw.w, (int)h4.w, ih[gq]);
-          il[gq] = dp4a_ss((int)kw.x, (int)l4.x, il[gq]);
-          il[gq] = dp4a_ss((int)kw.y, (int)l4.y, il[gq]);
-          il[gq] = dp4a_ss((int)kw.z, (int)l4.z, il[gq]);
-          il[gq] = dp4a_ss((int)kw.w, (int)l4.w, il[gq]);
-        }
+      for (int gq = 0; gq < G; ++gq) {
+        const uint4 h4 = *reinterpret_cast<const uint4*>(qhi + gq * hd + 16 * c);
+        const uint4 l4 = *reinterpret_cast<const uint4*>(qlo + gq * hd + 16 * c);
+        ih[gq] = dp4a_ss((int)kw.x, (int)h4.x, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.y, (int)h4.y, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.z, (int)h4.z, ih[gq]);
+        ih[gq] = dp4a_ss((int)kw.w, (int)h4.w, ih[gq]);
+        il[gq] = dp4a_ss((int)kw.x, (int)l4.x, il[gq]);
+        il[gq] = dp4a_ss((int)kw.y, (int)l4.y, il[gq]);
+        il[gq] = dp4a_ss((int)kw.z, (int)l4.z, il[gq]);
+        il[gq] = dp4a_ss((int)kw.w, (int)l4.w, il[gq]);
       }
     }
 #pragma unroll
@@ -346,14 +288,13 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   }
   // --- softmax inside the partition; the G heads share each block-wide reduction
   __shared__ float s_redm[PA_MAX_GROUP * (NT / 32)], s_reds[PA_MAX_GROUP * (NT / 32)];
-  const int warp_i = tid >> 5, lane_i = tid & 31;
   float pmax[G], psum[G];
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) {
     float m = lmax[gq];
 #pragma unroll
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if (lane_i == 0) s_redm[gq * (NT / 32) + warp_i] = m;
+    if (lane == 0) s_redm[gq * (NT / 32) + warp] = m;
   }
   __syncthreads();
 #pragma unroll
@@ -365,7 +306,8 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     psum[gq] = 0.f;
   }
   for (uint32_t i = tid; i < n; i += NT) {
-    const float vsc = vscs[i];
+    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
+    const float vsc = reinterpret_cast<const float*>(rec + a.g.vs_off())[i % bs];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) {
       float e = expf(prob[gq * a.part_tokens + i] - pmax[gq]);
@@ -378,7 +320,7 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     float t = psum[gq];
 #pragma unroll
     for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
-    if (lane_i == 0) s_reds[gq * (NT / 32) + warp_i] = t;
+    if (lane == 0) s_reds[gq * (NT / 32) + warp] = t;
   }
   __syncthreads();  // also: every probability is written before PV reads them
 #pragma unroll
@@ -389,36 +331,31 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     psum[gq] = t;
   }
 
-  // --- PV
+  // --- PV: thread = (8 dims = one 64-bit word c of the V row, token slice)
+  const uint32_t dwords = hd / 8;
+  const uint32_t nslice = NT / dwords;  // hd in {16..256} -> dwords in {2..32}
+  const uint32_t c = tid % dwords, slice = tid / dwords;
   float acc[G][8];
 #pragma unroll
   for (int gq = 0; gq < G; ++gq)
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[gq][k] = 0.f;
-  for (uint32_t i0 = slice; i0 < n; i0 += 4 * nslice) {
-    uint2 vnext[4];
-    load_v(i0 + 4 * nslice, vnext);  // nothing is loaded past the partition's end
+  for (uint32_t i = slice; i < n; i += nslice) {
+    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
+    const uint2 vw = reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(i % bs) * hd)[c];
+    const uint32_t lo = vw.x ^ 0x80808080u, hi = vw.y ^ 0x80808080u;
+    float f[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t i = i0 + j * nslice;
-      if (i < n) {
-        const uint32_t lo = vcur[j].x ^ 0x80808080u, hi = vcur[j].y ^ 0x80808080u;
-        float f[8];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          f[k] = s8_to_f32(lo, k);
-          f[4 + k] = s8_to_f32(hi, k);
-        }
-#pragma unroll
-        for (int gq = 0; gq < G; ++gq) {
-          const float p = prob[gq * a.part_tokens + i];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[gq][k] = fmaf(p, f[k], acc[gq][k]);
-        }
-      }
+    for (int k = 0; k < 4; ++k) {
+      f[k] = s8_to_f32(lo, k);
+      f[4 + k] = s8_to_f32(hi, k);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) vcur[j] = vnext[j];
+    for (int gq = 0; gq < G; ++gq) {
+      const float p = prob[gq * a.part_tokens + i];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[gq][k] = fmaf(p, f[k], acc[gq][k]);
+    }
   }
   // reduce over token slices through shared memory: red[slice][G][hd]
   float4* red4 = reinterpret_cast<float4*>(red);
@@ -566,14 +503,15 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
   return KANSO_OK;
 }
 
-// Dynamic shared memory of stage 1: query planes and scales, block ids, probabilities,
-// V scales, PV reduction scratch.
+// Dynamic shared memory of stage 1: the partition's block records, query planes and scales,
+// block ids, probabilities, PV reduction scratch.
 static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t block_size,
-                             uint32_t threads) {
-  const uint32_t nblk_part = ((pt + block_size - 1) / block_size + 4) & ~3u;
+                             uint32_t rec_bytes, uint32_t threads) {
+  const uint32_t max_blk = (pt + block_size - 1) / block_size;
+  const uint32_t nblk_part = (max_blk + 4) & ~3u;
   const uint32_t dwords = hd / 8, nslice = threads / dwords;
-  size_t smem = 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 + (size_t)((G * pt + 3) & ~3u) * 4 +
-                (size_t)((pt + 3) & ~3u) * 4;
+  size_t smem = (size_t)max_blk * rec_bytes + 16 + 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 +
+                (size_t)((G * pt + 3) & ~3u) * 4;
   size_t red_bytes = (size_t)nslice * G * hd * 4;
   if (red_bytes < 128) red_bytes = 128;
   return smem + red_bytes;
@@ -593,7 +531,10 @@ static void launch_stage1_nt(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, si
 }
 template <int G>
 static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
-  launch_stage1_nt<G, PA_THREADS>(ctx, a, grid, smem);
+  if (pa_threads(a.part_tokens) == PA_BIG_THREADS)
+    launch_stage1_nt<G, PA_BIG_THREADS>(ctx, a, grid, smem);
+  else
+    launch_stage1_nt<G, PA_THREADS>(ctx, a, grid, smem);
 }
 
 int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
@@ -610,7 +551,11 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
                         2ull * ctx->sm_count)
     pt >>= 1;
-  // whole blocks per partition keep the per-partition block list simple
+  // the partition's records are staged in shared memory: two CTAs per SM when possible
+  while (pt > 64 &&
+         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt)) > (size_t)ctx->smem_optin / 2)
+    pt >>= 1;
+  // whole blocks per partition: a partition starts on a block record
   if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
   const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
@@ -652,7 +597,7 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
     a.table_len = fusion->table_len;
   }
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, PA_THREADS);
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt));
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: %zu bytes of shared memory needed",
                 smem);
@@ -784,6 +729,9 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
                         2ull * ctx->sm_count)
     pt >>= 1;
+  while (pt > 64 &&
+         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt)) > (size_t)ctx->smem_optin / 2)
+    pt >>= 1;
   if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
 
@@ -824,7 +772,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.positions = a.slots = nullptr;
   a.table_len = 0;
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, PA_THREADS);
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt));
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "paged_attention_noalloc: %zu bytes of shared memory needed", smem);
