@@ -549,7 +549,7 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
   uint32_t pt = 512;
   while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
-                        2ull * ctx->sm_count)
+                        (uint64_t)ctx->sm_count / 2)
     pt >>= 1;
   // the partition's records are staged in shared memory: two CTAs per SM when possible
   while (pt > 64 &&
@@ -727,7 +727,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
   uint32_t pt = 512;
   while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
-                        2ull * ctx->sm_count)
+                        (uint64_t)ctx->sm_count / 2)
     pt >>= 1;
   while (pt > 64 &&
          pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt)) > (size_t)ctx->smem_optin / 2)
