@@ -55,6 +55,23 @@ struct PaArgs {
   int table_len;
 };
 
+// (block, offset) of token i = i0, i0 + step, ... inside a partition, without a division per
+// token (the block size is a run-time value).
+struct PaTokenIter {
+  uint32_t blk, off, adv_blk, adv_off, bs;
+  __device__ __forceinline__ PaTokenIter(uint32_t i0, uint32_t step, uint32_t block_size)
+      : blk(i0 / block_size), off(i0 % block_size), adv_blk(step / block_size),
+        adv_off(step % block_size), bs(block_size) {}
+  __device__ __forceinline__ void next() {
+    blk += adv_blk;
+    off += adv_off;
+    if (off >= bs) {
+      off -= bs;
+      ++blk;
+    }
+  }
+};
+
 __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
   // biased_word = bytes ^ 0x80 (value + 128). Put byte k into the low mantissa bits of 2^23.
   uint32_t bits = __byte_perm(biased_word, 0x4B000000u, 0x7540 | k);
@@ -254,9 +271,10 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   float lmax[G];
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) lmax[gq] = -INFINITY;
-  for (uint32_t i = tid; i < n; i += NT) {
-    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
-    const uint32_t off = i % bs;
+  PaTokenIter qk_it(tid, NT, bs);
+  for (uint32_t i = tid; i < n; i += NT, qk_it.next()) {
+    const uint8_t* rec = tiles + (size_t)qk_it.blk * a.g.rec_bytes;
+    const uint32_t off = qk_it.off;
     const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
     const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
     int ih[G], il[G];
@@ -305,9 +323,10 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     pmax[gq] = m;
     psum[gq] = 0.f;
   }
-  for (uint32_t i = tid; i < n; i += NT) {
-    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
-    const float vsc = reinterpret_cast<const float*>(rec + a.g.vs_off())[i % bs];
+  PaTokenIter sm_it(tid, NT, bs);
+  for (uint32_t i = tid; i < n; i += NT, sm_it.next()) {
+    const uint8_t* rec = tiles + (size_t)sm_it.blk * a.g.rec_bytes;
+    const float vsc = reinterpret_cast<const float*>(rec + a.g.vs_off())[sm_it.off];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) {
       float e = expf(prob[gq * a.part_tokens + i] - pmax[gq]);
@@ -340,9 +359,11 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   for (int gq = 0; gq < G; ++gq)
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[gq][k] = 0.f;
-  for (uint32_t i = slice; i < n; i += nslice) {
-    const uint8_t* rec = tiles + (size_t)(i / bs) * a.g.rec_bytes;
-    const uint2 vw = reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)(i % bs) * hd)[c];
+  PaTokenIter pv_it(slice, nslice, bs);
+  for (uint32_t i = slice; i < n; i += nslice, pv_it.next()) {
+    const uint8_t* rec = tiles + (size_t)pv_it.blk * a.g.rec_bytes;
+    const uint2 vw =
+        reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)pv_it.off * hd)[c];
     const uint32_t lo = vw.x ^ 0x80808080u, hi = vw.y ^ 0x80808080u;
     float f[8];
 #pragma unroll
