@@ -115,6 +115,7 @@ int32_t kanso_cuda_ctx_create(int32_t device, void* stream, kanso_cuda_ctx** out
   }
   e = cudaMalloc(&ctx->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_status, sizeof(int));
   if (e == cudaSuccess)
     e = cudaMalloc(&ctx->pa_tickets, sizeof(uint32_t) * kanso_cuda_ctx::kPaTickets);
   if (e == cudaSuccess)
@@ -136,6 +137,7 @@ int32_t kanso_cuda_ctx_destroy(kanso_cuda_ctx* ctx) {
   if (ctx->stage_dev) cudaFree(ctx->stage_dev);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->host_status) cudaFreeHost(ctx->host_status);
   if (ctx->pa_tickets) cudaFree(ctx->pa_tickets);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -144,10 +146,13 @@ int32_t kanso_cuda_ctx_destroy(kanso_cuda_ctx* ctx) {
 
 int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx) {
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "sync: ctx is NULL");
-  KANSO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream), "stream synchronize");
-  int st = 0;
-  KANSO_CUDA_TRY(ctx, cudaMemcpy(&st, ctx->dev_status, sizeof st, cudaMemcpyDeviceToHost),
+  // the status word rides behind the stream's work into pinned memory: one wait for both
+  KANSO_CUDA_TRY(ctx,
+                 cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int),
+                                 cudaMemcpyDeviceToHost, ctx->stream),
                  "status word read");
+  KANSO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream), "stream synchronize");
+  const int st = *ctx->host_status;
   if (st != 0) {
     cudaMemset(ctx->dev_status, 0, sizeof(int));
     // a kernel that gave up may have left attention tickets taken

@@ -14,6 +14,7 @@ struct kanso_cuda_ctx {
   int sm_count = 0;
   int smem_optin = 0;      // max dynamic shared memory per block (opt-in), bytes
   int* dev_status = nullptr;  // one int on the device, OR of kanso::DevStatus
+  int* host_status = nullptr;  // pinned: the status word lands here with the stream's other work
   // arrival counters of the split-context attention (one per sequence and KV head); all zero
   // between calls: the CTA that takes the last ticket of a counter resets it
   uint32_t* pa_tickets = nullptr;
