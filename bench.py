@@ -3,12 +3,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1]): W_up[14336x4096] and W_down[4096x14336], GGUF
+Workload (Llama-3-8B-like FFN shapes): W_up[14336x4096] and W_down[4096x14336], GGUF
 Q4_K super-blocks quantised from seeded N(0, 0.02) weights, f32 activations from
 N(0, 1), y = W.x. One step = one GEMV over each matrix of a ring of distinct
 (up, down) pairs whose total size is several times the 126 MB L2, so every launch
 streams its weights from HBM. The step is captured in a CUDA graph so that the
-~5 us kernels run back to back instead of at the host's launch rate.
+~12 us kernels run back to back instead of at the host's launch rate. The line also
+carries `other_paths`: the Q8_0 GEMV, the batched GEMM and the decode step, timed the same way.
 
 Prints ONE JSON line (rank 0). `value` counts algorithmic bytes
 (weights once + x + y per launch) over the device time of the timed steps.
