@@ -342,6 +342,13 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        # A rank that never joins (or a stalled exchange) would leave the others waiting for
+        # ever: every rank ends itself after a deadline well beyond a normal run.
+        deadline = threading.Timer(float(os.environ.get("KANSO_BENCH_DEADLINE_S", "420")),
+                                   lambda: (sys.stderr.write("bench: deadline passed, exiting\n"),
+                                            os._exit(3)))
+        deadline.daemon = True
+        deadline.start()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     kb = importlib.import_module("kanso-infer_b200").backend

@@ -131,6 +131,37 @@ def test_q8_0_tensor_core_gemv_edges(ctx, kb, oracle, torch_cuda, M, N, K):
                    oracle.gemm_q8_0(b8, x, M, N, K, 1)) <= 1e-5
 
 
+def test_k_shard_exchange_on_one_gpu(ctx, kb, oracle, torch_cuda):
+    """The two halves of a K-sharded linear, run as two "ranks" on one GPU: each stores its
+    partial result into its slice of the shared buffer through the scatter entry point, then
+    kanso_cuda_sum_shards adds the slices in rank order."""
+    import ctypes as C
+    sh = __import__("importlib").import_module("kanso-infer_b200").sharded
+    torch = torch_cuda
+    rng = np.random.Generator(np.random.PCG64(0xB2000D00))
+    rows, cols, world = 264, 1024, 2
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    blocks = oracle.quantize_weights_q4_k(w)
+    for M in (1, 3):
+        x = rng.standard_normal((M, cols)).astype(np.float32)
+        ref = oracle.gemm_q4_k(blocks, x, M, rows, cols)
+        xd = dev(torch, x)
+        parts = torch.full((M, world * rows), float("nan"), dtype=torch.float32, device="cuda")
+        ptrs = (C.c_void_p * 1)(parts.data_ptr())
+        keep = []
+        for r in range(world):
+            shard, cb, cc = sh.k_shard(blocks, kb.DTYPE_Q4_K, rows, cols, r, world)
+            wt = kb.Weight(ctx, shard, kb.DTYPE_Q4_K, rows, cc)
+            keep.append(wt)
+            xs = xd[:, cb:cb + cc].contiguous()
+            ctx.call("kanso_cuda_linear_scatter_out", wt.h, kb._ptr(xs), M,
+                     C.cast(ptrs, C.c_void_p), 1, world * rows, r * rows, kb.ACT_F32)
+        y = torch.empty((M, rows), dtype=torch.float32, device="cuda")
+        ctx.call("kanso_cuda_sum_shards", kb._ptr(parts), M, rows, world, kb._ptr(y))
+        ctx.sync()
+        assert rel_err(y.cpu().numpy(), ref) <= TOL
+
+
 def test_linearity_at_full_size(ctx, kb, oracle, torch_cuda):
     """Size-independent property at the benchmark shape: W(ax + by) = a Wx + b Wy."""
     torch = torch_cuda
