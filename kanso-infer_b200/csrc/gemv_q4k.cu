@@ -87,43 +87,61 @@ __device__ __forceinline__ uint32_t pack4i(float a, float b, float c, float d) {
          (((uint32_t)(int)c & 0xFF) << 16) | (((uint32_t)(int)d & 0xFF) << 24);
 }
 
-// One warp per 256-value block: lane l owns values [8l, 8l+8).
+// The calling warp stages the activation planes of super-blocks [s_first, s_last] of every
+// activation row: the ones its own work items use (a neighbouring warp may stage a shared
+// boundary super-block too; both write the same bytes). Lane l owns values [8l, 8l+8) of a
+// 256-value block. The loads of up to four blocks are issued before any is processed.
 __device__ __forceinline__ void q4k_stage_activations(const Q4kArgs& a, const Q4kLayout& L,
-                                                      uint8_t* smem) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+                                                      uint8_t* smem, int s_first, int s_last) {
+  const int lane = threadIdx.x & 31;
   const int nsb = a.K / 256;
   float* dxs = reinterpret_cast<float*>(smem + L.off_dxs);
   float* xsum = reinterpret_cast<float*>(smem + L.off_sum);
-  for (int b = warp; b < a.M * nsb; b += nwarps) {
-    const int m = b / nsb, sb = b - m * nsb;
-    const float4* src =
-        reinterpret_cast<const float4*>(a.x + (int64_t)m * a.ldx + (int64_t)sb * 256) + 2 * lane;
-    const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
-    float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
-                       fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-    float sum = ((v0.x + v0.y) + (v0.z + v0.w)) + ((v1.x + v1.y) + (v1.z + v1.w));
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+  const int ns = s_last - s_first + 1;
+  const int total = ns * a.M;  // (activation row, super-block) pairs, row-major in m
+  for (int base = 0; base < total; base += 4) {
+    float4 v0[4], v1[4];
 #pragma unroll
-    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float d = amax * (1.0f / 127.0f);
-    const float id = d != 0.0f ? 1.0f / d : 0.0f;
-    const float il = 254.0f * id;
-    float h[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w}, l[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float xv = h[k];
-      h[k] = fminf(fmaxf(rintf(xv * id), -127.f), 127.f);
-      l[k] = fminf(fmaxf(rintf(fmaf(-d, h[k], xv) * il), -127.f), 127.f);
+    for (int j = 0; j < 4; ++j) {
+      const int b = min(base + j, total - 1);
+      const int m = b / ns, sb = s_first + (b - m * ns);
+      const float4* src =
+          reinterpret_cast<const float4*>(a.x + (int64_t)m * a.ldx + (int64_t)sb * 256) + 2 * lane;
+      v0[j] = __ldg(src);
+      v1[j] = __ldg(src + 1);
     }
-    uint8_t* p0 = smem + L.off_planes + (m * 2) * L.plane_stride + sb * 256 + 8 * lane;
-    *reinterpret_cast<uint2*>(p0) =
-        make_uint2(pack4i(h[0], h[1], h[2], h[3]), pack4i(h[4], h[5], h[6], h[7]));
-    *reinterpret_cast<uint2*>(p0 + L.plane_stride) =
-        make_uint2(pack4i(l[0], l[1], l[2], l[3]), pack4i(l[4], l[5], l[6], l[7]));
-    if ((lane & 3) == 0) xsum[m * (a.K / 32) + sb * 8 + (lane >> 2)] = sum;
-    // low-nibble sums enter with a factor 16 (see the kernel), hence 1/(254*16)
-    if (lane == 0) dxs[m * nsb + sb] = d * (1.0f / (254.0f * 16.0f));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (base + j >= total) break;
+      const int b = base + j;
+      const int m = b / ns, sb = s_first + (b - m * ns);
+      const float4 u0 = v0[j], u1 = v1[j];
+      float amax = fmaxf(fmaxf(fmaxf(fabsf(u0.x), fabsf(u0.y)), fmaxf(fabsf(u0.z), fabsf(u0.w))),
+                         fmaxf(fmaxf(fabsf(u1.x), fabsf(u1.y)), fmaxf(fabsf(u1.z), fabsf(u1.w))));
+      float sum = ((u0.x + u0.y) + (u0.z + u0.w)) + ((u1.x + u1.y) + (u1.z + u1.w));
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float d = amax * (1.0f / 127.0f);
+      const float id = d != 0.0f ? 1.0f / d : 0.0f;
+      const float il = 254.0f * id;
+      float h[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w}, l[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float xv = h[k];
+        h[k] = fminf(fmaxf(rintf(xv * id), -127.f), 127.f);
+        l[k] = fminf(fmaxf(rintf(fmaf(-d, h[k], xv) * il), -127.f), 127.f);
+      }
+      uint8_t* p0 = smem + L.off_planes + (m * 2) * L.plane_stride + sb * 256 + 8 * lane;
+      *reinterpret_cast<uint2*>(p0) =
+          make_uint2(pack4i(h[0], h[1], h[2], h[3]), pack4i(h[4], h[5], h[6], h[7]));
+      *reinterpret_cast<uint2*>(p0 + L.plane_stride) =
+          make_uint2(pack4i(l[0], l[1], l[2], l[3]), pack4i(l[4], l[5], l[6], l[7]));
+      if ((lane & 3) == 0) xsum[m * (a.K / 32) + sb * 8 + (lane >> 2)] = sum;
+      // low-nibble sums enter with a factor 16 (see the kernel), hence 1/(254*16)
+      if (lane == 0) dxs[m * nsb + sb] = d * (1.0f / (254.0f * 16.0f));
+    }
   }
 }
 
@@ -228,8 +246,9 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float* ypart = reinterpret_cast<float*>(smem + L.off_yacc);  // [M][bpr][max_rows]
-  q4k_stage_activations(a, L, smem);
-  __syncthreads();
+  // each warp stages only the super-blocks of the activations that its own items read
+  if (i0 < i1) q4k_stage_activations(a, L, smem, i0 / ngroups, (i1 - 1) / ngroups);
+  __syncwarp();
 
   const float* dxs = reinterpret_cast<const float*>(smem + L.off_dxs);
   const float* xsum = reinterpret_cast<const float*>(smem + L.off_sum);
