@@ -140,7 +140,7 @@ def test_decode_batch_of_ragged_sequences(ctx, kb, oracle, torch_cuda):
     assert e.value.code == kb.ERR_SHAPE
 
 
-@pytest.mark.parametrize("B,overlap", [(3, 1), (3, 0), (12, 1)])
+@pytest.mark.parametrize("B,overlap", [(1, 1), (2, 1), (3, 1), (3, 0), (12, 1)])
 def test_decode_smollm2_shapes(kb, oracle, torch_cuda, B, overlap):
     """SmolLM2-360M layer geometry (hidden 960, 15 query / 5 KV heads, head_dim 64, SwiGLU 2560,
     vocab 49152, RoPE theta 100000, 16-token blocks, permuted block tables), two layers, ragged
@@ -217,8 +217,13 @@ def test_decode_smollm2_shapes(kb, oracle, torch_cuda, B, overlap):
         blk, off = int(slots[s]) // bs, int(slots[s]) % bs
         _, o = opool.read_token(L - 1, blk, off)
         gtok = gpool.read_token(L - 1, blk, off)
-        assert np.mean(gtok["k_q"] != o["k_q"]) <= 0.02  # activations differ by ~1e-5: rare ties
-        assert np.allclose(gtok["k_scale"], o["k_scale"], rtol=1e-4)
+        # The layer's input differs from the CPU path's by the matmul tolerance (~1e-4 of the
+        # scale), so a value that lies within that of a rounding boundary may land on the
+        # other side: never by more than one step, and only for a small share of the bytes.
+        dq = gtok["k_q"].astype(np.int32) - o["k_q"].astype(np.int32)
+        assert np.max(np.abs(dq)) <= 1
+        assert np.mean(dq != 0) <= 0.10
+        assert np.allclose(gtok["k_scale"], o["k_scale"], rtol=1e-3)  # the matmul tolerance
     gm.destroy()
     gpool.destroy()
     ctx.close()
