@@ -82,9 +82,13 @@ __host__ __device__ inline Q4kLayout q4k_layout(int K, int M, int max_rows_cta, 
   return L;
 }
 
+// Four integral floats in [-128, 127] -> their int8 bytes, a in the lowest byte.
 __device__ __forceinline__ uint32_t pack4i(float a, float b, float c, float d) {
-  return ((uint32_t)(int)a & 0xFF) | (((uint32_t)(int)b & 0xFF) << 8) |
-         (((uint32_t)(int)c & 0xFF) << 16) | (((uint32_t)(int)d & 0xFF) << 24);
+  uint32_t lo, out;
+  // cvt.pack: d = (sat8(x) << 8 | sat8(y)) | (z << 16)
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"((int)b), "r"((int)a), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"((int)d), "r"((int)c), "r"(0));
+  return lo | (out << 16);
 }
 
 // The calling warp stages the activation planes of super-blocks [s_first, s_last] of every
@@ -130,8 +134,10 @@ __device__ __forceinline__ void q4k_stage_activations(const Q4kArgs& a, const Q4
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const float xv = h[k];
-        h[k] = fminf(fmaxf(rintf(xv * id), -127.f), 127.f);
-        l[k] = fminf(fmaxf(rintf(fmaf(-d, h[k], xv) * il), -127.f), 127.f);
+        // |xv * id| <= 127 and |residual * il| <= 127 by construction (up to an ulp that
+        // rounds away): no clamps
+        h[k] = rintf(xv * id);
+        l[k] = rintf(fmaf(-d, h[k], xv) * il);
       }
       uint8_t* p0 = smem + L.off_planes + (m * 2) * L.plane_stride + sb * 256 + 8 * lane;
       *reinterpret_cast<uint2*>(p0) =
