@@ -34,7 +34,7 @@ UP = (14336, 4096)    # rows (N), cols (K)
 DOWN = (4096, 14336)
 Q4K_BYTES, QK_K = 144, 256
 SEED = 0xB2000000 + 2 * 100
-NCU_DRAM_BYTES_PER_LAUNCH = 33_109_760
+NCU_DRAM_BYTES_PER_LAUNCH = 33_105_664
 
 
 def alg_bytes(rows, cols):
