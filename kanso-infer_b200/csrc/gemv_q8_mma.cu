@@ -144,7 +144,6 @@ __global__ void __launch_bounds__(Q8M_THREADS, 2) gemv_q8_mma_kernel(const Q8mAr
   // pair. More rows: each lane quantises the k-words of its own MMA column.
   float nwv[NBT];
   if (COOP) {
-
     // The norm weights are weights: read before the wait. Lane = element of the block.
 #pragma unroll
     for (int j = 0; j < NBT; ++j)
@@ -153,7 +152,6 @@ __global__ void __launch_bounds__(Q8M_THREADS, 2) gemv_q8_mma_kernel(const Q8mAr
   pdl_launch_dependents();
   pdl_wait();
   if (COOP) {
-
     // ---- activation fragments of this warp's K slice. The 32 lanes quantise the 32 values of
     // one (activation row, block) pair together, one value each; the bytes are then gathered
     // into 32-bit words inside each quad of lanes and handed to the lanes that own the matching
