@@ -1,6 +1,9 @@
 // Context lifetime, error reporting, scratch management.
 #include "ctx.h"
 
+#include <mutex>
+#include <unordered_set>
+
 namespace {
 thread_local std::string g_no_ctx_error = "";
 }
@@ -64,6 +67,18 @@ int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes) {
   return KANSO_OK;
 }
 
+void prefer_max_shared(kanso_cuda_ctx* ctx, const void* kern) {
+  static std::mutex mu;
+  static std::unordered_set<uintptr_t> done;  // (kernel, device) pairs already set
+  const uintptr_t key = reinterpret_cast<uintptr_t>(kern) * 16u + (uintptr_t)(ctx->device & 15);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done.insert(key).second) return;
+  // a preference only: a refusal changes nothing about the result
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+    cudaGetLastError();
+}
+
 int32_t after_launch(kanso_cuda_ctx* ctx, const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(ctx, e, what);
@@ -103,6 +118,7 @@ int32_t kanso_cuda_ctx_create(int32_t device, void* stream, kanso_cuda_ctx** out
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
   ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  ctx->smem_per_sm = (int)prop.sharedMemPerMultiprocessor;
   if (stream) {
     ctx->stream = (cudaStream_t)stream;
   } else {

@@ -13,6 +13,7 @@ struct kanso_cuda_ctx {
   bool own_stream = false;
   int sm_count = 0;
   int smem_optin = 0;      // max dynamic shared memory per block (opt-in), bytes
+  int smem_per_sm = 0;     // shared memory of one SM, bytes
   int* dev_status = nullptr;  // one int on the device, OR of kanso::DevStatus
   int* host_status = nullptr;  // pinned: the status word lands here with the stream's other work
   // arrival counters of the split-context attention (one per sequence and KV head); all zero
@@ -58,9 +59,17 @@ int32_t after_launch(kanso_cuda_ctx* ctx, const char* what);
 // (KANSO_OPT_OVERLAP_WEIGHT_PREFETCH) the launch carries the programmatic-stream-serialization
 // attribute; such a kernel MUST execute griddepcontrol.wait before it touches anything an
 // earlier kernel may have written.
+//
+// Every kernel launched here asks for the largest shared-memory carveout, once per device. A
+// launch that overlaps the kernel before it can only share an SM with it when both run under
+// the same L1/shared split; with per-launch splits the SM drains and switches between kernels
+// of different shared-memory sizes. None of the kernels depends on a large L1.
+void prefer_max_shared(kanso_cuda_ctx* ctx, const void* kern);
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_dependent(kanso_cuda_ctx* ctx, void (*kern)(KArgs...), dim3 grid,
                                     dim3 block, size_t smem, Args&&... args) {
+  prefer_max_shared(ctx, reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t lc = {};
   lc.gridDim = grid;
   lc.blockDim = block;

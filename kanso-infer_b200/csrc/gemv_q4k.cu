@@ -8,9 +8,9 @@
 //     into groups of 8 rows; a work item is (row group, super-block) = 8 x 144 bytes. Items
 //     are ordered super-block-major and each warp takes a contiguous share of them, so the
 //     activation fragments of a super-block stay in registers over a run of items;
-//   * every warp runs its own ring of six shared-memory slots filled with 16-byte
-//     cp.async copies (8 rows x 9 pieces per item, whole sectors of each row), so about
-//     100 KB per SM is in flight without holding registers. Rows sit 160 bytes apart in a
+//   * every warp runs its own ring of three to five shared-memory slots filled with 16-byte
+//     cp.async copies (8 rows x 9 pieces per item, whole sectors of each row), so
+//     60-100 KB per SM are in flight without holding registers. Rows sit 160 bytes apart in a
 //     slot, which keeps the 64-bit fragment loads of a warp free of bank conflicts;
 //   * a lane (gid = lane / 4, t = lane % 4) works on row gid of the group: the 16-byte
 //     header (shared by the four lanes of a row) and, for each of the four 64-weight
@@ -54,6 +54,8 @@ struct Q4kArgs {
   int64_t rows, ldx, ldy;
   int K, bpr, M;
   int max_rows_cta;
+  // row groups per CTA: the first groups_rem CTAs take groups_quot + 1, the others groups_quot
+  int groups_quot, groups_rem;
 };
 
 struct Q4kLayout {
@@ -154,12 +156,12 @@ __device__ __forceinline__ void q4k_stage_activations(const Q4kArgs& a, const Q4
 // c = A*B (the accumulator input is zero)
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  c[0] = c[1] = c[2] = c[3] = 0;
+  // the zero goes in as one constant operand: no accumulator registers to clear per call
   asm volatile(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+      "{%10,%10,%10,%10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
@@ -194,10 +196,9 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   const int M = a.M, bpr = a.bpr, max_rows = a.max_rows_cta;
 
   // rows are dealt out in groups of 8 (the host guarantees rows % 8 == 0)
-  const int total_groups = (int)(a.rows >> 3);
-  const int g_begin = (int)((int64_t)total_groups * blockIdx.x / gridDim.x);
-  const int g_end = (int)((int64_t)total_groups * (blockIdx.x + 1) / gridDim.x);
-  const int ngroups = g_end - g_begin;
+  const int cta = (int)blockIdx.x;
+  const int g_begin = a.groups_quot * cta + min(cta, a.groups_rem);
+  const int ngroups = a.groups_quot + (cta < a.groups_rem ? 1 : 0);
   const int nrows = ngroups * 8;
   const int64_t rb = (int64_t)g_begin * 8;
   const uint32_t row_bytes = (uint32_t)bpr * Q4K_BYTES;
@@ -206,14 +207,15 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   // Items in super-block-major order, i = S * ngroups + g; each warp owns a contiguous range,
   // so its activation fragments change only when S does.
   const int n_items = ngroups * bpr;
-  const int i0 = (int)((int64_t)n_items * warp / Q4M_WARPS);
-  const int i1 = (int)((int64_t)n_items * (warp + 1) / Q4M_WARPS);
+  // (n_items < 2^24: at most 227 KB / 4 bytes of per-item partial sums fit in shared memory)
+  const int i0 = (int)((uint32_t)n_items * (uint32_t)warp / (uint32_t)Q4M_WARPS);
+  const int i1 = (int)((uint32_t)n_items * (uint32_t)(warp + 1) / (uint32_t)Q4M_WARPS);
 
   // copy roles: lane (gid, t) copies pieces t, t+4 and (t == 0) 8 of row gid: 64 contiguous
   // bytes per row and instruction, at constant offsets from one pointer per lane
   const uint32_t lane_g = (uint32_t)gid * row_bytes + 16u * t;
   const uint32_t lane_s = (uint32_t)gid * Q4M_ROW_STRIDE + 16u * t;
-  const uint32_t third = t == 0 ? 1u : 0u;
+  const bool third = t == 0;
   const uint32_t ring0 = smem_u32(smem + L.off_ring + warp * (Q4M_DEPTH * Q4M_SLOT));
   const uint32_t ring_end = ring0 + Q4M_DEPTH * Q4M_SLOT;
   const uint32_t gstep = 8u * row_bytes;
@@ -223,12 +225,14 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   auto issue = [&]() {
     if (li < i1) {
       asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.u32 p, %2, 0;\n"
           "cp.async.cg.shared.global [%0], [%1], 16;\n"
-          "cp.async.cg.shared.global [%0+64], [%1+64], 16;\n"
-          "@p cp.async.cg.shared.global [%0+128], [%1+128], 16;\n}\n" ::"r"(ldst + lane_s),
-          "l"(lsrc), "r"(third)
+          "cp.async.cg.shared.global [%0+64], [%1+64], 16;\n" ::"r"(ldst + lane_s),
+          "l"(lsrc)
           : "memory");
+      if (third)
+        asm volatile("cp.async.cg.shared.global [%0+128], [%1+128], 16;\n" ::"r"(ldst + lane_s),
+                     "l"(lsrc)
+                     : "memory");
       ++li;
       if (++lg == ngroups) {
         lg = 0;
@@ -267,9 +271,9 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   uint2 bf[MSETS][4];   // B fragments: [pair][low0, high0, low1, high1]
   float4 xs[MSETS];     // f32 sums of x over this lane's four sub-blocks
   float dx[MSETS];
-  uint32_t ok[MSETS];   // does this lane publish a result for activation-row pair ms?
+  bool ok[MSETS];       // does this lane publish a result for activation-row pair ms?
 #pragma unroll
-  for (int ms = 0; ms < MSETS; ++ms) ok[ms] = (plane == 0 && 2 * ms + out_m < M) ? 1u : 0u;
+  for (int ms = 0; ms < MSETS; ++ms) ok[ms] = plane == 0 && 2 * ms + out_m < M;
   auto load_x = [&](int S) {
 #pragma unroll
     for (int ms = 0; ms < MSETS; ++ms) {
@@ -338,11 +342,10 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
       mins = fmaf((float)(mw >> 24), xs[ms].w, mins);
       float v = fmaf(d * dx[ms], f, -dmin * mins);
       v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);  // hi plane + lo plane (and both halves of mins)
-      asm volatile(
-          "{\n.reg .pred p;\nsetp.ne.u32 p, %2, 0;\n@p st.shared.f32 [%0], %1;\n}\n" ::"r"(
-              yaddr + 8u * (uint32_t)(ms * bpr * max_rows)),
-          "f"(v), "r"(ok[ms])
-          : "memory");
+      if (ok[ms])
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(yaddr + 8u * (uint32_t)(ms * bpr * max_rows)),
+                     "f"(v)
+                     : "memory");
     }
     yaddr += 32u;
     if (++gg == ngroups) {
@@ -383,6 +386,7 @@ static int32_t launch_q4k_mma(kanso_cuda_ctx* ctx, const Q4kArgs& a, int grid, i
                    "gemv_q4k: shared memory opt-in");
     smem_set[ctx->device & 15] = ctx->smem_optin;
   }
+  prefer_max_shared(ctx, reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(grid);
   lc.blockDim = dim3(NW * 32);
@@ -407,14 +411,14 @@ static int32_t dispatch_q4k_msets(kanso_cuda_ctx* ctx, const Q4kArgs& a, int gri
   }
 }
 
-// Launch shape: warps per CTA, ring depth, CTAs per SM. KANSO_Q4K_CFG="warps,depth,ctas"
-// overrides the default for tuning runs.
+// Launch shape: warps per CTA, ring depth (0: chosen per launch), CTAs per SM.
+// KANSO_Q4K_CFG="warps,depth,ctas" overrides the default for tuning runs.
 struct Q4kCfg {
   int nw, depth, cps;
 };
 static Q4kCfg q4k_cfg() {
   static Q4kCfg cfg = [] {
-    Q4kCfg c{16, 5, 1};
+    Q4kCfg c{16, 0, 1};
     if (const char* e = getenv("KANSO_Q4K_CFG")) {
       int nw, d, cps;
       if (sscanf(e, "%d,%d,%d", &nw, &d, &cps) == 3) c = Q4kCfg{nw, d, cps};
@@ -441,10 +445,25 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
   *handled = false;
   if (n_out < 0 || n_out > Q4M_MAX_OUT) return KANSO_OK;
   if (K % 256 != 0 || M < 1 || M > 8 || N < 8 || N % 8 != 0) return KANSO_OK;
-  const Q4kCfg cfg = q4k_cfg();
+  Q4kCfg cfg = q4k_cfg();
   int grid = ctx->sm_count * cfg.cps;
   if (N / 8 < grid) grid = (int)(N / 8);  // every CTA gets at least one group of 8 rows
   const int max_rows_cta = (int)(((N / 8 + grid - 1) / grid) * 8);
+  if (cfg.depth == 0) {
+    // The deepest ring (5..3 slots per warp) with which two CTAs fit on an SM: under
+    // dependent-launch overlap the next GEMV's CTA then moves in beside this one and has its
+    // ring filled when this kernel ends, which is worth more than the fifth slot. Shapes whose
+    // activation planes leave no room for two CTAs take four slots.
+    cfg.depth = 4;
+    for (int d = 5; d >= 3; --d) {
+      // (1 KB per CTA is reserved by the system)
+      if (2 * (q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, d).total + 1024) <=
+          ctx->smem_per_sm) {
+        cfg.depth = d;
+        break;
+      }
+    }
+  }
   Q4kLayout L = q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, cfg.depth);
   if (L.total > ctx->smem_optin) return KANSO_OK;
   Q4kArgs a;
@@ -461,6 +480,8 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
   a.bpr = (int)(K / 256);
   a.M = (int)M;
   a.max_rows_cta = max_rows_cta;
+  a.groups_quot = (int)((N / 8) / grid);
+  a.groups_rem = (int)((N / 8) % grid);
   *handled = true;
   const int key = cfg.nw * 100 + cfg.depth;
   switch (key) {
