@@ -84,13 +84,27 @@ __host__ __device__ inline Q4kLayout q4k_layout(int K, int M, int max_rows_cta, 
   return L;
 }
 
-// Four integral floats in [-128, 127] -> their int8 bytes, a in the lowest byte.
-__device__ __forceinline__ uint32_t pack4i(float a, float b, float c, float d) {
-  uint32_t lo, out;
-  // cvt.pack: d = (sat8(x) << 8 | sat8(y)) | (z << 16)
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"((int)b), "r"((int)a), "r"(0));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"((int)d), "r"((int)c), "r"(0));
-  return lo | (out << 16);
+// Packed f32x2 arithmetic (two floats per 64-bit register, one instruction for both).
+__device__ __forceinline__ uint64_t f2pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// The lowest bytes of the four 32-bit halves of a and b, a's low half first.
+__device__ __forceinline__ uint32_t low_bytes4(uint64_t a, uint64_t b) {
+  const uint32_t p01 = __byte_perm((uint32_t)a, (uint32_t)(a >> 32), 0x0040);
+  const uint32_t p23 = __byte_perm((uint32_t)b, (uint32_t)(b >> 32), 0x0040);
+  return __byte_perm(p01, p23, 0x5410);
 }
 
 // The calling warp stages the activation planes of super-blocks [s_first, s_last] of every
@@ -132,20 +146,27 @@ __device__ __forceinline__ void q4k_stage_activations(const Q4kArgs& a, const Q4
       const float d = amax * (1.0f / 127.0f);
       const float id = d != 0.0f ? 1.0f / d : 0.0f;
       const float il = 254.0f * id;
-      float h[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w}, l[8];
+      // Rounding by the 1.5 * 2^23 trick: v + MAGIC has the integer nearest to v (ties to even)
+      // in its low mantissa bits, two's complement, so the int8 byte is the lowest byte of the
+      // float and no conversion instruction is needed. |x * id| <= 127 and
+      // |residual * il| <= 127 by construction (up to an ulp that rounds away): no clamps.
+      const float MAGIC = 12582912.0f;
+      const uint64_t magic2 = f2pack(MAGIC, MAGIC), nmagic2 = f2pack(-MAGIC, -MAGIC);
+      const uint64_t id2 = f2pack(id, id), il2 = f2pack(il, il), nd2 = f2pack(-d, -d);
+      const uint64_t xv[4] = {f2pack(u0.x, u0.y), f2pack(u0.z, u0.w), f2pack(u1.x, u1.y),
+                              f2pack(u1.z, u1.w)};
+      uint64_t th[4], tl[4];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float xv = h[k];
-        // |xv * id| <= 127 and |residual * il| <= 127 by construction (up to an ulp that
-        // rounds away): no clamps
-        h[k] = rintf(xv * id);
-        l[k] = rintf(fmaf(-d, h[k], xv) * il);
+      for (int k = 0; k < 4; ++k) {
+        th[k] = f2fma(xv[k], id2, magic2);                  // MAGIC + hi
+        const uint64_t hf = f2add(th[k], nmagic2);          // hi as a float
+        tl[k] = f2fma(f2fma(nd2, hf, xv[k]), il2, magic2);  // MAGIC + lo
       }
       uint8_t* p0 = smem + L.off_planes + (m * 2) * L.plane_stride + sb * 256 + 8 * lane;
       *reinterpret_cast<uint2*>(p0) =
-          make_uint2(pack4i(h[0], h[1], h[2], h[3]), pack4i(h[4], h[5], h[6], h[7]));
+          make_uint2(low_bytes4(th[0], th[1]), low_bytes4(th[2], th[3]));
       *reinterpret_cast<uint2*>(p0 + L.plane_stride) =
-          make_uint2(pack4i(l[0], l[1], l[2], l[3]), pack4i(l[4], l[5], l[6], l[7]));
+          make_uint2(low_bytes4(tl[0], tl[1]), low_bytes4(tl[2], tl[3]));
       if ((lane & 3) == 0) xsum[m * (a.K / 32) + sb * 8 + (lane >> 2)] = sum;
       // low-nibble sums enter with a factor 16 (see the kernel), hence 1/(254*16)
       if (lane == 0) dxs[m * nsb + sb] = d * (1.0f / (254.0f * 16.0f));
@@ -453,16 +474,12 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
     // The deepest ring (5..3 slots per warp) with which two CTAs fit on an SM: under
     // dependent-launch overlap the next GEMV's CTA then moves in beside this one and has its
     // ring filled when this kernel ends, which is worth more than the fifth slot. Shapes whose
-    // activation planes leave no room for two CTAs take four slots.
-    cfg.depth = 4;
-    for (int d = 5; d >= 3; --d) {
-      // (1 KB per CTA is reserved by the system)
-      if (2 * (q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, d).total + 1024) <=
-          ctx->smem_per_sm) {
-        cfg.depth = d;
-        break;
-      }
-    }
+    // activation planes leave no room for two CTAs take four slots, or three if four do not
+    // fit at all.
+    auto total = [&](int d) { return q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, d).total; };
+    for (int d = 5; d >= 3 && !cfg.depth; --d)
+      if (2 * (total(d) + 1024) <= ctx->smem_per_sm) cfg.depth = d;  // 1 KB per CTA is reserved
+    if (!cfg.depth) cfg.depth = total(4) <= ctx->smem_optin ? 4 : 3;
   }
   Q4kLayout L = q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, cfg.depth);
   if (L.total > ctx->smem_optin) return KANSO_OK;

@@ -131,6 +131,22 @@ def test_q8_0_tensor_core_gemv_edges(ctx, kb, oracle, torch_cuda, M, N, K):
                    oracle.gemm_q8_0(b8, x, M, N, K, 1)) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 512, 14336), (2, 512, 14336), (4, 512, 14336),
+                                   (6, 256, 8192), (3, 1192, 4096), (8, 512, 14336),
+                                   (7, 320, 4096), (8, 1192, 2048)])
+def test_q4_k_ring_depths(ctx, kb, oracle, torch_cuda, M, N, K):
+    """The Q4_K tensor-core GEMV sizes its copy rings by the shared memory the activation
+    planes leave: long K with several activation rows reaches the shallow rings (and the
+    shapes where two CTAs no longer share an SM), short K the deep ones. Seven and eight rows
+    go in passes of four."""
+    rng = np.random.Generator(np.random.PCG64(0xB2000900 + 977 * M + N + K))
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b4 = oracle.quantize_weights_q4_k(w)
+    assert rel_err(run_gemm(ctx, kb, torch_cuda, kb.DTYPE_Q4_K, b4, x, M, N, K),
+                   oracle.gemm_q4_k(b4, x, M, N, K)) <= TOL
+
+
 def test_k_shard_exchange_on_one_gpu(ctx, kb, oracle, torch_cuda):
     """The two halves of a K-sharded linear, run as two "ranks" on one GPU: each stores its
     partial result into its slice of the shared buffer through the scatter entry point, then
