@@ -412,21 +412,22 @@ def run_ours(args):
     if err > 1e-3:
         raise SystemExit(f"bench: GEMV result differs from the oracle by {err:.2e} (> 1e-3)")
 
+    # GEMV launches per step (at N > 1 each pair adds two exchanges and one shard sum)
     launches_per_step = 2 * pairs
 
     class _Eager:  # same interface as a captured graph, for steps that cannot be captured
         def replay(self):
             step()
 
-    if world == 1:
+    if world == 1 or not os.environ.get("KANSO_BENCH_EAGER"):
+        # at N > 1 the step holds only this library's kernels (the cross-GPU exchange is one of
+        # them and keeps its step number on the device), so it is captured like the N = 1 step
         launch_mode = "CUDA graph of the step"
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             step()
     else:
-        # the collectives (NCCL all-reduce, symmetric-memory barrier) are launched step by
-        # step: a capture of them stalled in a 2-GPU trial, so they stay out of a graph
-        graph, launch_mode = _Eager(), "eager launches (collectives are not captured)"
+        graph, launch_mode = _Eager(), "eager launches"
     for _ in range(max(3, args.warmup)):
         graph.replay()
     torch.cuda.synchronize()
@@ -529,7 +530,7 @@ def run_ours(args):
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
                      "kernel": "gemv_q4k_mma_kernel", "us_per_launch": us_per_launch,
                      "alg_bytes_per_launch": per_launch_bytes},
-        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": (launches_per_step if world == 1 else 5 * pairs) * args.steps, "clocks": clocks,
     }
     if cpu:
         line["cpu_baseline"] = cpu

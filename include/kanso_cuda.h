@@ -212,6 +212,15 @@ int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weig
  * order: y[m, n] = sum_r parts[m, r * rows + n]. No counterpart in the reference. */
 int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M, int64_t rows,
                               int32_t world, float* y);
+/* The cross-GPU barrier of the two sharded forms above, as one small kernel on the context's
+ * stream: tells every peer that this rank's stores of the step are done and waits (at most
+ * 2 s, then KANSO_ERR_TIMEOUT at the next kanso_cuda_sync) until every peer has said the same.
+ * flags[r] (r < world <= 8): rank r's array of `world` u64 slots, zeroed once, mapped into this
+ * process (symmetric memory); step: one u64 in this GPU's memory, zeroed once, advanced by
+ * every call. Every rank makes the same sequence of calls; no host state, so the calls can be
+ * captured in a CUDA graph. No counterpart in the reference. */
+int32_t kanso_cuda_peer_exchange(kanso_cuda_ctx* ctx, void* const* flags, void* step,
+                                 int32_t world, int32_t rank);
 /* LinearWeight::embed — src/weights.rs:50-57: dequantise the selected rows.
  * ids u32[T] (device), out f32[T, cols] (device). An id >= rows -> KANSO_ERR_SHAPE
  * is reported by the device status word at the next kanso_cuda_sync. */

@@ -81,6 +81,7 @@ PROTOTYPES = {
     "kanso_cuda_shard_k_repack": (_I32, [_P, _I32, _I64, _I64, _I64, _I64, _P, _SZ]),
     "kanso_cuda_linear_scatter_out": (_I32, [_P, _P, _P, _I64, _P, _I32, _I64, _I64, _I32]),
     "kanso_cuda_sum_shards": (_I32, [_P, _P, _I64, _I64, _I32, _P]),
+    "kanso_cuda_peer_exchange": (_I32, [_P, _P, _P, _I32, _I32]),
     "kanso_cuda_kv_create": (_I32, [_P, _U32, _U32, _U32, _U32, _U32, _I32, C.POINTER(_P)]),
     "kanso_cuda_kv_destroy": (_I32, [_P]),
     "kanso_cuda_kv_write_slots": (_I32, [_P, _P, _U32, _P, _P, _P, _I64, _P]),

@@ -8,7 +8,10 @@
 // Blocks never straddle a shard: ranges are multiples of the block size (and of 8 rows).
 #include <cstring>
 
+#include "common.cuh"
 #include "ctx.h"
+
+#define KANSO_MAX_PEERS 8
 
 namespace kanso {
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
@@ -38,6 +41,10 @@ using namespace kanso;
 // bits).
 __global__ void sum_shards_kernel(const float* __restrict__ parts, int64_t M, int64_t rows,
                                   int world, float* __restrict__ y) {
+  // launched while the exchange before it still waits for the peers; nothing is read before
+  // that kernel has ended
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * rows) return;
   const int64_t m = i / rows, n = i - m * rows;
@@ -47,7 +54,86 @@ __global__ void sum_shards_kernel(const float* __restrict__ parts, int64_t M, in
   y[i] = s;
 }
 
+// One thread per rank. Thread r tells rank r that this rank's stores of the current step are
+// done (release store of the step number into slot `rank` of rank r's flag array), then waits
+// until rank r has said the same to this rank (slot r of the own array). The step number lives
+// in device memory and advances by one per call, so a captured graph of calls stays valid
+// across replays; every rank makes the same sequence of calls. The wait is bounded by wall
+// time: a peer that never arrives ends it with DEV_WAIT_TIMEOUT in the status word.
+struct ExchangeArgs {
+  unsigned long long* flags[KANSO_MAX_PEERS];  // flags[r]: rank r's array of `world` slots
+  unsigned long long* step;                   // this rank's step counter
+  int world, rank;
+  unsigned long long timeout_ns;
+  int* status;
+};
+__device__ __forceinline__ void peer_exchange(const ExchangeArgs& a, unsigned long long* s_step) {
+  // Programmatic dependent launch: the kernel after this one (a GEMV) may start at once and
+  // fetch its first weight tiles while this one waits for the peers; it reads nothing an
+  // earlier kernel wrote before its own griddepcontrol.wait, which this kernel's end releases.
+  pdl_launch_dependents();
+  pdl_wait();  // the kernels before this one are complete, their stores performed
+  const int r = threadIdx.x;
+  if (r == 0) *s_step = *a.step + 1;
+  __syncthreads();
+  const unsigned long long e = *s_step;
+  if (r < a.world) {
+    // make the stores of the earlier kernels to the peers visible before the flag is
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.flags[r] + a.rank), "l"(e)
+                 : "memory");
+    const unsigned long long* mine = a.flags[a.rank] + r;
+    unsigned long long t0, t1, seen;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+      if (seen >= e) break;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t1 - t0 > a.timeout_ns) {
+        atomicOr(a.status, (int)DEV_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  if (r == 0) *a.step = e;
+}
+
+__global__ void peer_exchange_kernel(const ExchangeArgs a) {
+  __shared__ unsigned long long s_step;
+  peer_exchange(a, &s_step);
+}
+
+static int32_t exchange_args(kanso_cuda_ctx* ctx, void* const* flags, void* step, int32_t world,
+                             int32_t rank, ExchangeArgs* a, const char* who) {
+  if (!flags || !step || world < 1 || world > KANSO_MAX_PEERS || rank < 0 || rank >= world)
+    return fail(ctx, KANSO_ERR_SHAPE, "%s: bad arguments (world %d, rank %d)", who, world, rank);
+  *a = ExchangeArgs{};
+  for (int r = 0; r < world; ++r) {
+    if (!flags[r]) return fail(ctx, KANSO_ERR_SHAPE, "%s: flags[%d] is NULL", who, r);
+    a->flags[r] = (unsigned long long*)flags[r];
+  }
+  a->step = (unsigned long long*)step;
+  a->world = world;
+  a->rank = rank;
+  a->timeout_ns = 2000000000ull;  // 2 s
+  a->status = ctx->dev_status;
+  return KANSO_OK;
+}
+
 extern "C" {
+
+int32_t kanso_cuda_peer_exchange(kanso_cuda_ctx* ctx, void* const* flags, void* step,
+                                 int32_t world, int32_t rank) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "peer_exchange: ctx is NULL");
+  ExchangeArgs a;
+  int32_t st = exchange_args(ctx, flags, step, world, rank, &a, "peer_exchange");
+  if (st) return st;
+  KANSO_CUDA_TRY(ctx, launch_dependent(ctx, peer_exchange_kernel, dim3(1), dim3(32), 0, a),
+                 "peer_exchange launch");
+  return after_launch(ctx, "peer_exchange");
+}
 
 int32_t kanso_cuda_shard_range(int64_t n, int32_t rank, int32_t world, int64_t align,
                                int64_t* begin, int64_t* count) {
@@ -134,7 +220,10 @@ int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M
                 (long long)M, (long long)rows, world);
   const int64_t n = M * rows;
   if (n == 0) return KANSO_OK;
-  sum_shards_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(parts, M, rows, world, y);
+  KANSO_CUDA_TRY(ctx,
+                 launch_dependent(ctx, sum_shards_kernel, dim3((unsigned)((n + 255) / 256)),
+                                  dim3(256), 0, parts, M, rows, world, y),
+                 "sum_shards launch");
   return after_launch(ctx, "sum_shards");
 }
 

@@ -55,6 +55,40 @@ def k_shard(blocks: np.ndarray, dtype: int, rows: int, cols: int, rank: int, wor
     return out, begin, count
 
 
+class PeerExchange:
+    """The flag arrays and step counter of kanso_cuda_peer_exchange for one process group:
+    the cross-GPU barrier of the fused sharded layers as a kernel on the context's stream."""
+
+    _by_group = {}
+
+    @classmethod
+    def get(cls, ctx, group):
+        key = (id(ctx), group.group_name)
+        if key not in cls._by_group:
+            cls._by_group[key] = cls(ctx, group)
+        return cls._by_group[key]
+
+    def __init__(self, ctx, group):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.ctx = ctx
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise kb.KansoError(kb.ERR_UNSUPPORTED, "peer exchange: at most 8 ranks")
+        self.flags = symm.empty((self.world,), dtype=torch.int64, device="cuda")
+        self.flags.zero_()
+        self._hdl = symm.rendezvous(self.flags, group.group_name)
+        self._ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        self.step = torch.zeros(1, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every rank's flags are zero before anyone signals
+
+    def __call__(self):
+        self.ctx.call("kanso_cuda_peer_exchange", C.cast(self._ptrs, C.c_void_p),
+                      kb._ptr(self.step), self.world, self.rank)
+
+
 class RowShardedLinear:
     """W[rows x cols] split by output rows; forward returns the full y on every rank."""
 
@@ -87,6 +121,7 @@ class RowShardedLinear:
                 self._hdls.append(hdl)
                 self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
             self.y_full = self._bufs[0]
+            self._exchange = PeerExchange.get(ctx, self.group)
         elif mode == "nccl":
             self.y_full = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
             self.y_local = torch.empty((max_m, self.row_count), dtype=torch.float32, device="cuda")
@@ -99,13 +134,13 @@ class RowShardedLinear:
         if M > self.max_m:
             raise kb.KansoError(kb.ERR_SHAPE, f"M {M} exceeds the buffers sized for {self.max_m}")
         if self.mode == "fused":
-            # every rank stores its slice into every rank's y_full, then one barrier
+            # every rank stores its slice into every rank's y_full, then one exchange
             t = self._turn
             self._turn ^= 1
             self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x), M,
                           C.cast(self._ptrs[t], C.c_void_p), self.world, self.rows,
                           self.row_begin, act_mode)
-            self._hdls[t].barrier(channel=0)
+            self._exchange()
             self.y_full = self._bufs[t]
             return self.y_full[:M]
         y_local = self.y_local[:M]
@@ -157,6 +192,7 @@ class KShardedLinear:
                 self._bufs.append(buf)
                 self._hdls.append(hdl)
                 self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
+            self._exchange = PeerExchange.get(ctx, self.group)
         elif mode != "nccl":
             raise ValueError(mode)
 
@@ -166,13 +202,13 @@ class KShardedLinear:
         y = self.y[:M]
         if self.mode == "fused":
             # every rank stores its partial y into its slice of every rank's buffer; after
-            # one barrier each rank adds the slices itself, in rank order
+            # one exchange each rank adds the slices itself, in rank order
             t = self._turn
             self._turn ^= 1
             self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x_slice), M,
                           C.cast(self._ptrs[t], C.c_void_p), self.world, self.world * self.rows,
                           self.rank * self.rows, act_mode)
-            self._hdls[t].barrier(channel=0)
+            self._exchange()
             self.ctx.call("kanso_cuda_sum_shards", kb._ptr(self._bufs[t]), M, self.rows,
                           self.world, kb._ptr(y))
             return y

@@ -178,6 +178,35 @@ def test_k_shard_exchange_on_one_gpu(ctx, kb, oracle, torch_cuda):
         assert rel_err(y.cpu().numpy(), ref) <= TOL
 
 
+def test_peer_exchange_single_rank_and_give_up(ctx, kb, torch_cuda):
+    """kanso_cuda_peer_exchange on one GPU. With one rank it signals itself: the step counter
+    and the flag advance by one per call. With a second rank that never signals (its flag
+    array is just a second buffer here) the wait runs out after its 2 s limit: the signal
+    was sent, the next sync reports KANSO_ERR_TIMEOUT, and the context stays usable."""
+    import ctypes as C
+    torch = torch_cuda
+    flags = torch.zeros(1, dtype=torch.int64, device="cuda")
+    step = torch.zeros(1, dtype=torch.int64, device="cuda")
+    ptrs = (C.c_void_p * 1)(flags.data_ptr())
+    for _ in range(3):
+        ctx.call("kanso_cuda_peer_exchange", C.cast(ptrs, C.c_void_p), kb._ptr(step), 1, 0)
+    ctx.sync()
+    assert int(step.item()) == 3 and int(flags.item()) == 3
+
+    mine = torch.zeros(2, dtype=torch.int64, device="cuda")
+    absent = torch.zeros(2, dtype=torch.int64, device="cuda")
+    step.zero_()
+    ptrs2 = (C.c_void_p * 2)(mine.data_ptr(), absent.data_ptr())
+    ctx.call("kanso_cuda_peer_exchange", C.cast(ptrs2, C.c_void_p), kb._ptr(step), 2, 0)
+    with pytest.raises(kb.KansoError) as ei:
+        ctx.sync()
+    assert ei.value.code == kb.ERR_TIMEOUT
+    assert mine.tolist() == [1, 0] and absent.tolist() == [1, 0]
+    ctx.call("kanso_cuda_peer_exchange", C.cast(ptrs, C.c_void_p), kb._ptr(step), 1, 0)
+    ctx.sync()
+    assert int(flags.item()) == 2  # step was 1 after the call that gave up
+
+
 def test_linearity_at_full_size(ctx, kb, oracle, torch_cuda):
     """Size-independent property at the benchmark shape: W(ax + by) = a Wx + b Wy."""
     torch = torch_cuda
