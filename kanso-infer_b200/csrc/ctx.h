@@ -55,21 +55,22 @@ int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes);
 // Checks the launch, counts it.
 int32_t after_launch(kanso_cuda_ctx* ctx, const char* what);
 
+// Asks, once per device, for the largest shared-memory carveout for `kern`. A launch that
+// overlaps the kernel before it can only share an SM with it when both run under the same
+// L1/shared split; with per-launch splits the SM drains and switches between launches of
+// different shared-memory sizes. For kernels that stage through shared memory and do not
+// depend on a large L1 (the Q4_K GEMV); the Q8_0 tensor-core GEMV reads its activations
+// through L1 and keeps the default split (42.5 against 37 us at 8 rows with the large
+// carveout).
+void prefer_max_shared(kanso_cuda_ctx* ctx, const void* kern);
+
 // Launches `kern` on the context's stream. When the context allows overlap
 // (KANSO_OPT_OVERLAP_WEIGHT_PREFETCH) the launch carries the programmatic-stream-serialization
 // attribute; such a kernel MUST execute griddepcontrol.wait before it touches anything an
 // earlier kernel may have written.
-//
-// Every kernel launched here asks for the largest shared-memory carveout, once per device. A
-// launch that overlaps the kernel before it can only share an SM with it when both run under
-// the same L1/shared split; with per-launch splits the SM drains and switches between kernels
-// of different shared-memory sizes. None of the kernels depends on a large L1.
-void prefer_max_shared(kanso_cuda_ctx* ctx, const void* kern);
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_dependent(kanso_cuda_ctx* ctx, void (*kern)(KArgs...), dim3 grid,
                                     dim3 block, size_t smem, Args&&... args) {
-  prefer_max_shared(ctx, reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t lc = {};
   lc.gridDim = grid;
   lc.blockDim = block;
