@@ -200,7 +200,8 @@ int32_t kanso_cuda_shard_k_repack(const void* host_bytes, int32_t dtype, int64_t
  * y[m, row_offset + r] is stored into every one of the n_out (<= 8) result buffers
  * y_out[i] (f32 [M, n_total]; this GPU's own and its peers' buffers mapped into this
  * process, e.g. symmetric memory). Stores to peers are plain stores over NVLink; the caller
- * orders them against the readers with its usual cross-GPU barrier. */
+ * orders them against the readers with a cross-GPU barrier (kanso_cuda_peer_exchange below is
+ * one, as a kernel on the same stream). */
 int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
                                       const float* x, int64_t M, float* const* y_out,
                                       int32_t n_out, int64_t n_total, int64_t row_offset,
@@ -208,7 +209,7 @@ int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weig
 /* K sharding with the reduction done through the same peer stores: every rank stores its
  * partial y into slice [rank * rows, (rank + 1) * rows) of every rank's parts buffer
  * (f32 [M, world * rows]) with kanso_cuda_linear_scatter_out(n_total = world * rows,
- * row_offset = rank * rows); after the caller's cross-GPU barrier this adds the slices in rank
+ * row_offset = rank * rows); after the cross-GPU barrier (kanso_cuda_peer_exchange) this adds the slices in rank
  * order: y[m, n] = sum_r parts[m, r * rows + n]. No counterpart in the reference. */
 int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M, int64_t rows,
                               int32_t world, float* y);
