@@ -209,8 +209,9 @@ int32_t kanso_cuda_linear_scatter_out(kanso_cuda_ctx* ctx, const kanso_cuda_weig
 /* K sharding with the reduction done through the same peer stores: every rank stores its
  * partial y into slice [rank * rows, (rank + 1) * rows) of every rank's parts buffer
  * (f32 [M, world * rows]) with kanso_cuda_linear_scatter_out(n_total = world * rows,
- * row_offset = rank * rows); after the cross-GPU barrier (kanso_cuda_peer_exchange) this adds the slices in rank
- * order: y[m, n] = sum_r parts[m, r * rows + n]. No counterpart in the reference. */
+ * row_offset = rank * rows); after the cross-GPU barrier (kanso_cuda_peer_exchange) this
+ * adds the slices in rank order: y[m, n] = sum_r parts[m, r * rows + n]. No counterpart in
+ * the reference. */
 int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M, int64_t rows,
                               int32_t world, float* y);
 /* The cross-GPU barrier of the two sharded forms above, as one small kernel on the context's
