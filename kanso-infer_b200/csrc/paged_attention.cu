@@ -18,6 +18,8 @@
 // array the merge runs inside stage 1, in the CTA that finishes last for its (sequence, kv head):
 // every CTA publishes its partials, fences, and takes a ticket; the one that draws the last
 // ticket reads all partials back. Nothing waits on anything, so there is no spin to bound.
+#include <mutex>
+
 #include "glue.cuh"
 #include "kv_pool.h"
 
@@ -78,6 +80,23 @@ __device__ __forceinline__ float s8_to_f32(uint32_t biased_word, int k) {
   return __uint_as_float(bits) - 8388736.0f;  // 2^23 + 128
 }
 
+// The context length a launch can serve: the table's capacity (max_blocks * block_size; the
+// reference rejects a longer context on the host, src/metal/paged_attention.rs:343-355) and the
+// window of partitions this grid was sized for. A device length beyond either is cut off there
+// (the reference's kernel clamps its partition range the same way,
+// src/metal/kernels/paged_attention_v2.metal:86-87) and reported through the status word, so no
+// table entry, partial or scratch cell outside the launch's own range is ever addressed.
+__device__ __forceinline__ uint32_t pa_clamp_ctx(const PaArgs& a, uint32_t ctx, bool report) {
+  const uint64_t cap = (uint64_t)a.max_blocks * a.g.block_size;
+  const uint64_t window = (uint64_t)a.num_parts * a.part_tokens;
+  const uint64_t lim = cap < window ? cap : window;
+  if ((uint64_t)ctx > lim) {
+    if (report) atomicOr(a.status, DEV_BAD_INDEX);
+    ctx = (uint32_t)lim;
+  }
+  return ctx;
+}
+
 // NT = threads per CTA.
 template <int G, int NT>
 __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
@@ -99,6 +118,7 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     pdl_wait();  // q, the table and the lengths may come from earlier kernels
     ctx = a.lens[seq];
   }
+  ctx = pa_clamp_ctx(a, ctx, part == 0 && kvh == 0 && threadIdx.x == 0);
   const uint32_t t0 = part * a.part_tokens;
   if (ctx == 0 && a.tickets && part == 0) {
     // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
@@ -473,14 +493,15 @@ __global__ void paged_attn_stage2(const PaArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t head = blockIdx.x, seq = blockIdx.y, hd = a.g.head_dim;
-  const uint32_t ctx = a.lens[seq];
+  // the same cut-off as stage 1: only partitions that stage 1 wrote are read
+  const uint32_t ctx = pa_clamp_ctx(a, a.lens[seq], false);
   const size_t hidx = (size_t)seq * a.num_heads + head;
   float* o = a.out + hidx * hd;
   if (ctx == 0) {  // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
     for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) o[d] = 0.f;
     return;
   }
-  const uint32_t np = (ctx + a.part_tokens - 1) / a.part_tokens;
+  const uint32_t np = min((ctx + a.part_tokens - 1) / a.part_tokens, a.num_parts);
   const float* ml = a.part_ml + hidx * a.num_parts * 2;
   float M = -INFINITY;
   for (uint32_t p = 0; p < np; ++p) M = fmaxf(M, ml[2 * p]);
@@ -713,20 +734,30 @@ static __device__ __align__(256) unsigned char g_pa_static_scratch[PA_STATIC_SCR
 // Device address of the array, looked up once per device. In host code the symbol's name is
 // only a handle for the runtime, not a device pointer, so it must never be handed to a kernel
 // directly; cudaGetSymbolAddress translates it for the device that is current.
+// Contexts are single-caller, but two contexts on different threads may make their first calls
+// at the same time: the table is filled under a mutex. The caller's current device is put back
+// before returning.
 static unsigned char* pa_static_scratch_ptr(kanso_cuda_ctx* ctx, int32_t* status) {
   static unsigned char* per_device[64] = {nullptr};
+  static std::mutex mu;
   *status = KANSO_OK;
   const int dev = ctx->device;
   if (dev < 0 || dev >= 64) {
     *status = fail(ctx, KANSO_ERR_UNSUPPORTED, "paged_attention_noalloc: device index %d", dev);
     return nullptr;
   }
+  std::lock_guard<std::mutex> lock(mu);
   if (!per_device[dev]) {
     int cur = -1;
     cudaError_t e = cudaGetDevice(&cur);
-    if (e == cudaSuccess && cur != dev) e = cudaSetDevice(dev);
+    const bool switched = e == cudaSuccess && cur != dev;
+    if (switched) e = cudaSetDevice(dev);
     unsigned char* p = nullptr;
     if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&p, g_pa_static_scratch);
+    if (switched) {
+      const cudaError_t back = cudaSetDevice(cur);
+      if (e == cudaSuccess) e = back;
+    }
     if (e != cudaSuccess || !p) {
       *status = cuda_fail(ctx, e, "paged_attention_noalloc: cudaGetSymbolAddress");
       return nullptr;

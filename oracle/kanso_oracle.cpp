@@ -452,6 +452,17 @@ int32_t kanso_ref_kv_write_token(kanso_ref_kv* kv, uint32_t layer, uint32_t bloc
   return ST_OK;
 }
 
+int32_t kanso_ref_kv_write_slots(kanso_ref_kv* kv, uint32_t layer, const uint32_t* slots,
+                                 const float* k, const float* v, int64_t T) {
+  const size_t row = (size_t)kv->kv_heads * kv->head_dim;
+  for (int64_t t = 0; t < T; ++t) {
+    int32_t st = kanso_ref_kv_write_token(kv, layer, slots[t] / kv->block_size,
+                                          slots[t] % kv->block_size, k + t * row, v + t * row);
+    if (st != ST_OK) return st;
+  }
+  return ST_OK;
+}
+
 void kanso_ref_kv_reset_block(kanso_ref_kv* kv, uint32_t block) {
   if (block >= kv->num_blocks) return;
   for (uint32_t l = 0; l < kv->layers; ++l) {

@@ -94,6 +94,10 @@ void kanso_ref_kv_destroy(kanso_ref_kv* kv);
 /* write_quantized_kv_token (quantized_storage.rs:143-204); status as the C ABI's. */
 int32_t kanso_ref_kv_write_token(kanso_ref_kv* kv, uint32_t layer, uint32_t block,
                                  uint32_t offset, const float* k, const float* v);
+/* KvStorageKind::write_kv_slots (src/kv_cache/kind.rs:348): T tokens, slot = block*block_size +
+ * offset (kind.rs:111), k and v f32[T, kvh*hd]; each token through write_quantized_kv_token. */
+int32_t kanso_ref_kv_write_slots(kanso_ref_kv* kv, uint32_t layer, const uint32_t* slots,
+                                 const float* k, const float* v, int64_t T);
 /* reset_block (quantized_storage.rs:134-140). */
 void kanso_ref_kv_reset_block(kanso_ref_kv* kv, uint32_t block);
 /* read_quantized_kv_token (quantized_storage.rs:219-270). Any output may be NULL. */

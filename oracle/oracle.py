@@ -267,6 +267,11 @@ class KvPool:
         return lib().kanso_ref_kv_write_token(self.h, C.c_uint32(layer), C.c_uint32(block),
                                               C.c_uint32(offset), _p(k), _p(v))
 
+    def write_slots(self, layer, slots, k, v):
+        slots, k, v = _u32(slots), _f32(k), _f32(v)
+        return lib().kanso_ref_kv_write_slots(self.h, C.c_uint32(layer), _p(slots), _p(k), _p(v),
+                                              C.c_int64(slots.size))
+
     def reset_block(self, block):
         lib().kanso_ref_kv_reset_block(self.h, C.c_uint32(block))
 

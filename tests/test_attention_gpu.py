@@ -92,6 +92,7 @@ def random_case(rng, S, H, KH, hd, bs, lens, NB):
     (1, 8, 1, 128, 16, [100]),            # group 8, head_dim 128
     (1, 5, 1, 256, 16, [70]),             # group 5, head_dim 256
     (4, 2, 2, 16, 4, [1, 2, 3, 9]),       # tiny heads, context 1
+    (2, 15, 5, 64, 16, [4096, 3000]),     # the longest context of the decode benchmark
 ])
 def test_paged_attention_matches_oracle(ctx, kb, oracle, torch_cuda, S, H, KH, hd, bs, lens):
     torch = torch_cuda
@@ -136,3 +137,112 @@ def test_paged_attention_errors(ctx, kb, torch_cuda):
         ctx.sync()
     assert e.value.code == kb.ERR_SHAPE
     ctx.sync()  # the status word is cleared once reported
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+@pytest.mark.parametrize("group", [1, 4, 5, 8])
+def test_paged_attention_reference_parity_matrix(ctx, kb, oracle, torch_cuda, hd, group):
+    """The reference's parity matrix, head_dim {64, 128, 256} x GQA group {1, 4, 5, 8}, with its
+    closed-form inputs and its non-contiguous table (tests/test_paged_attention_v2.rs:326-401).
+    The reference runs it over an f32 cache; here every cache row goes through the int8 pool's
+    quantiser on both sides, and the oracle's attention over that pool is the expected value."""
+    torch = torch_cuda
+    S, KH, bs, maxb, NB = 2, 2, 16, 4, 10
+    H = KH * group
+    lens = np.array([37, 16], np.uint32)
+    q = ((np.arange(S * H * hd) % 17).astype(np.float32) - 8.0) * np.float32(0.125)
+    n = NB * bs * KH * hd
+    kc = ((np.arange(n) % 19).astype(np.float32) - 9.0) * np.float32(0.1)
+    vc = ((np.arange(n) % 23).astype(np.float32) - 11.0) * np.float32(0.15)
+    tables = np.array([5, 2, 7, 0, 3, 9, 1, 6], np.uint32)
+    slots = np.arange(NB * bs, dtype=np.uint32)
+    gp, op = kb.KvPool(ctx, 1, NB, bs, KH, hd), oracle.KvPool(1, NB, bs, KH, hd)
+    k2, v2 = kc.reshape(NB * bs, KH * hd), vc.reshape(NB * bs, KH * hd)
+    gp.write_slots(0, dev(torch, slots), dev(torch, k2), dev(torch, v2), slots.size, slots)
+    assert op.write_slots(0, slots, k2, v2) == 0
+    scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+    p = kb.PagedAttentionParams(S, H, KH, hd, bs, maxb, scale)
+    out = torch.full((S, H * hd), float("nan"), dtype=torch.float32, device="cuda")
+    gp.paged_attention(0, dev(torch, q.reshape(S, H * hd)), dev(torch, tables), dev(torch, lens),
+                       out, p, lens)
+    ctx.sync()
+    st, ref = oracle.paged_attention_int8(op, 0, q, tables, lens,
+                                          oracle.PaParams(S, H, KH, hd, bs, maxb, scale))
+    assert st == 0
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-3
+    # against the reference's own f32-cache expectation the int8 pool costs about a percent
+    f32 = oracle.paged_attention_f32(q, kc, vc, tables, lens,
+                                     oracle.PaParams(S, H, KH, hd, bs, maxb, scale))
+    assert rel_err(out.cpu().numpy().reshape(-1), f32) <= 3e-2
+    gp.destroy()
+
+
+def test_paged_attention_flat_context_2048(ctx, kb, oracle, torch_cuda):
+    """The reference's 2048-token case (tests/test_paged_attention_v2.rs:559-633): constant q,
+    K and V, identity table; the output is finite, positive and equals V's constant."""
+    torch = torch_cuda
+    S, H, KH, hd, bs, ctx_len = 1, 4, 4, 64, 16, 2048
+    maxb = ctx_len // bs
+    NB = maxb + 4
+    slots = np.arange(ctx_len, dtype=np.uint32)
+    k = np.full((ctx_len, KH * hd), 0.05, np.float32)
+    v = np.full((ctx_len, KH * hd), 0.02, np.float32)
+    gp = kb.KvPool(ctx, 1, NB, bs, KH, hd)
+    gp.write_slots(0, dev(torch, slots), dev(torch, k), dev(torch, v), ctx_len, slots)
+    q = np.full((S, H * hd), 0.1, np.float32)
+    lens = np.array([ctx_len], np.uint32)
+    p = kb.PagedAttentionParams(S, H, KH, hd, bs, maxb, 0.125)
+    out = torch.full((S, H * hd), float("nan"), dtype=torch.float32, device="cuda")
+    gp.paged_attention(0, dev(torch, q), dev(torch, np.arange(maxb, dtype=np.uint32)),
+                       dev(torch, lens), out, p, lens)
+    ctx.sync()
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all() and (got > 0).all()
+    assert np.max(np.abs(got - 0.02)) <= 2e-5
+    gp.destroy()
+
+
+@pytest.mark.parametrize("entry", ["paged_attention", "paged_attention_noalloc"])
+def test_device_length_beyond_the_launch_is_cut_off_and_reported(ctx, kb, oracle, torch_cuda,
+                                                                 entry):
+    """A device-side context length larger than what the launch was sized for (the host's hint,
+    or the table's capacity when no hint is given) never reaches memory outside the launch's
+    own partials or table rows: both kernels cut it off at the same place, the result is the
+    attention over the tokens that remain, and the status word turns the next sync into a shape
+    error. The reference rejects such a length on the host (src/metal/paged_attention.rs:343-355)
+    and its kernel clamps the partition range (paged_attention_v2.metal:86-87)."""
+    torch = torch_cuda
+    S, H, KH, hd, bs = 1, 15, 5, 64, 16
+    rng = np.random.Generator(np.random.PCG64(0xB2000500))
+    stored = 704
+    NB = stored // bs + 3
+    maxb, tables, writes, q = random_case(rng, S, H, KH, hd, bs, [stored], NB)
+    gp, op = fill_pools(kb, ctx, oracle, torch, 1, NB, bs, KH, hd, writes)
+    p = kb.PagedAttentionParams(S, H, KH, hd, bs, maxb, 0.125)
+    call = getattr(gp, entry)
+    # (a) the host says 100 tokens, the device array says 700: the grid covers 128
+    out = torch.full((S, H * hd), float("nan"), dtype=torch.float32, device="cuda")
+    call(0, dev(torch, q), dev(torch, tables), dev(torch, np.array([700], np.uint32)), out, p,
+         np.array([100], np.uint32))
+    with pytest.raises(kb.KansoError) as e:
+        ctx.sync()
+    assert e.value.code == kb.ERR_SHAPE
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    cut = [c for c in (64, 128, 192, 256, 512) if c >= 100]
+    refs = [oracle.paged_attention_int8(op, 0, q, tables, np.array([c], np.uint32),
+                                        oracle.PaParams(S, H, KH, hd, bs, maxb, 0.125))[1]
+            for c in cut]
+    assert min(rel_err(got, r) for r in refs) <= 1e-3  # cut off at a whole partition
+    # (b) no host lengths, device length beyond the table's capacity: cut off at the capacity
+    out = torch.full((S, H * hd), float("nan"), dtype=torch.float32, device="cuda")
+    call(0, dev(torch, q), dev(torch, tables), dev(torch, np.array([maxb * bs + 40], np.uint32)),
+         out, p)
+    with pytest.raises(kb.KansoError) as e:
+        ctx.sync()
+    assert e.value.code == kb.ERR_SHAPE
+    _, ref = oracle.paged_attention_int8(op, 0, q, tables, np.array([maxb * bs], np.uint32),
+                                         oracle.PaParams(S, H, KH, hd, bs, maxb, 0.125))
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-3
+    ctx.sync()  # reported once, then clear
+    gp.destroy()

@@ -1,0 +1,146 @@
+"""GPU: parity at the sizes the benchmark configurations are quoted on.
+
+The scalar oracle cannot finish a 512 x 14336 x 4096 product in seconds, so the big matmuls are
+checked on a seeded sample of weight rows: every output column y[:, n] depends only on row n of
+the weight matrix (src/quant/q8_0.rs:82-92), so the oracle runs on the sampled rows' blocks and
+all M activation rows, while the GPU runs the whole matrix. The sample always holds the first
+and last rows of the matrix and rows on both sides of a 128-row tile edge.
+"""
+import numpy as np
+import pytest
+
+from cases import dev, fill_history, history_slots, permuted_tables, smollm2_models
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+K = 4096
+
+_weights = {}
+
+
+def quantized(oracle, kb, ctx, fmt, N):
+    """Seeded N(0, 0.02) weights [N x 4096] quantised once per (format, N) and kept on the GPU."""
+    key = (fmt, N)
+    if key not in _weights:
+        rng = np.random.Generator(np.random.PCG64(0xB2000300 + N + (1 if fmt == "q4_k" else 0)))
+        w = rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)
+        if fmt == "q8_0":
+            blocks, dtype, bpr = oracle.quantize_weights_q8_0(w), kb.DTYPE_Q8_0, K // 32 * 34
+        else:
+            blocks, dtype, bpr = oracle.quantize_weights_q4_k(w), kb.DTYPE_Q4_K, K // 256 * 144
+        _weights[key] = (blocks.reshape(N, bpr), kb.Weight(ctx, blocks, dtype, N, K))
+    return _weights[key]
+
+
+def sample_rows(rng, N, count=48):
+    fixed = [0, 1, 7, 8, 127, 128, 129, N - 129, N - 128, N - 9, N - 8, N - 1]
+    return np.unique(np.concatenate([np.array(fixed), rng.integers(0, N, count)]))
+
+
+@pytest.mark.parametrize("M", [8, 32, 128, 512])
+@pytest.mark.parametrize("N", [4096, 14336])
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_batched_matmul_at_config_shapes(ctx, kb, oracle, torch_cuda, fmt, N, M):
+    torch = torch_cuda
+    rows2d, W = quantized(oracle, kb, ctx, fmt, N)
+    rng = np.random.Generator(np.random.PCG64(0xB2000310 + M * 31 + N))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    W.forward(dev(torch, x), y, M)
+    ctx.sync()
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    pick = sample_rows(rng, N)
+    sub = np.ascontiguousarray(rows2d[pick]).reshape(-1)
+    ref = (oracle.gemm_q8_0 if fmt == "q8_0" else oracle.gemm_q4_k)(sub, x, M, pick.size, K)
+    scale = float(np.max(np.abs(got)))  # the scale of the whole result, not of the sample
+    err = float(np.max(np.abs(got[:, pick] - ref))) / scale
+    assert err <= TOL, f"{fmt} M={M} N={N}: {err:.2e}"
+
+
+@pytest.mark.parametrize("M", [8, 32, 128])
+def test_q8_activation_mode_at_config_shapes(ctx, kb, oracle, torch_cuda, M):
+    """KANSO_ACT_Q8: activations quantised per 32 by quantize_row_q8_0 and integer-dotted
+    (src/quant/q8_0.rs:43-66); the f32 result differs from the oracle only by the order of the
+    f32 block additions."""
+    torch = torch_cuda
+    N = 4096
+    rows2d, W = quantized(oracle, kb, ctx, "q8_0", N)
+    rng = np.random.Generator(np.random.PCG64(0xB2000330 + M))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    W.forward(dev(torch, x), y, M, kb.ACT_Q8)
+    ctx.sync()
+    got = y.cpu().numpy()
+    pick = sample_rows(rng, N)
+    ref = oracle.gemm_q8_0(np.ascontiguousarray(rows2d[pick]).reshape(-1), x, M, pick.size, K,
+                           oracle.ACT_Q8)
+    assert np.isfinite(got).all()
+    assert float(np.max(np.abs(got[:, pick] - ref))) / float(np.max(np.abs(got))) <= 1e-5
+
+
+def test_q8_0_gemv_1024_against_dense(ctx, kb, oracle, torch_cuda):
+    """The reference's own 1024 x 1024 case at its own size and bound: closed-form int8 pattern,
+    d = 0.015, x = sin(0.02 i), every row within 1e-2 (absolute) of the dense f32 product
+    (tests/test_neon_simd_gemv.rs:191-274). The GGUF block stores d as f16, so the dense
+    matrix is built from that same rounded d."""
+    torch = torch_cuda
+    rows = cols = 1024
+    r = np.arange(rows)[:, None, None]
+    b = np.arange(cols // 32)[None, :, None]
+    i = np.arange(32)[None, None, :]
+    q = (((r * 17 + b * 11 + i * 3) % 255) - 128).astype(np.int8)
+    d16 = np.float16(0.015)
+    blocks = np.zeros((rows, cols // 32, 34), np.uint8)
+    blocks[:, :, :2] = np.frombuffer(d16.tobytes(), np.uint8)
+    blocks[:, :, 2:] = q.view(np.uint8)
+    dense = (np.float32(d16) * q.astype(np.float32)).reshape(rows, cols)
+    x = np.sin(np.arange(cols, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    expect = np.cumsum(dense * x[None, :], axis=1, dtype=np.float32)[:, -1]  # sequential f32 sum
+    W = kb.Weight(ctx, blocks.reshape(-1), kb.DTYPE_Q8_0, rows, cols)
+    y = torch.empty(rows, dtype=torch.float32, device="cuda")
+    W.forward(dev(torch, x), y, 1)
+    ctx.sync()
+    got = y.cpu().numpy()
+    assert np.max(np.abs(got - expect)) < 1e-2
+    assert np.max(np.abs(oracle.gemv_q8_0(blocks.reshape(-1), x, rows, cols) - expect)) < 1e-2
+    W.free()
+
+
+@pytest.mark.parametrize("B", [8, 32, 64])
+def test_decode_step_at_config_batches(kb, oracle, torch_cuda, B):
+    """Benchmark configuration 4 at its batch sizes and context range, on TWO of the 32 layers
+    (the oracle's scalar lm_head over 49152 x 960 dominates its run time; the layers repeat the
+    same kernels): SmolLM2-360M geometry, Q8_0 weights, int8 paged KV with 16-token blocks and
+    permuted tables, contexts uniform in [256, 4096] with the extremes forced in. Logits within
+    1e-2 (absolute) of the oracle engine and the same greedy token
+    (src/model.rs:1101-1231, src/sampler.rs:7-17)."""
+    torch = torch_cuda
+    ctx = kb.Context(0, torch.cuda.current_stream())
+    ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 1)
+    L, bs, KH, hd, vocab = 2, 16, 5, 64, 49152
+    rng = np.random.Generator(np.random.PCG64(0xB2000400 + B))
+    om, gm = smollm2_models(kb, oracle, ctx, rng, L)
+    lens = [int(c) for c in rng.integers(256, 4097, size=B)]
+    lens[0], lens[-1] = 4096, 256
+    NB, tables = permuted_tables(rng, lens, bs)
+    opool, gpool = oracle.KvPool(L, NB, bs, KH, hd), kb.KvPool(ctx, L, NB, bs, KH, hd)
+    fill_history(torch, rng, gpool, opool, L, history_slots(tables, lens, bs), KH * hd)
+    st, maxb, padded = oracle.padded_decode_tables(bs, tables, lens)
+    assert st == 0 and maxb == 256
+    tokens = rng.integers(0, vocab, B).astype(np.uint32)
+    positions = np.array([c - 1 for c in lens], np.uint32)
+    slots = np.array([tables[s][(c - 1) // bs] * bs + (c - 1) % bs for s, c in enumerate(lens)],
+                     np.uint32)
+    st, ref = om.decode_step(opool, tokens, positions, slots, padded, lens, maxb)
+    assert st == 0
+    got = np.empty((B, vocab), np.float32)
+    gm.decode_step(gpool, tokens, positions, slots, padded, np.array(lens, np.uint32), maxb, got)
+    assert np.isfinite(got).all()
+    err = float(np.max(np.abs(got - ref)))
+    assert err <= 1e-2, f"B={B}: max |dlogit| {err:.2e}"
+    assert [int(np.argmax(r)) for r in got] == [oracle.greedy_token(r) for r in ref]
+    gm.destroy()
+    gpool.destroy()
+    ctx.close()
