@@ -1,0 +1,596 @@
+// Batched quantized GEMM with TMA-staged weight tiles (cp.async.bulk.tensor) feeding
+// tcgen05 / TMEM: LinearWeight::forward for continuous-batching and chunked-prefill rows
+// (src/weights.rs:43-45; callers src/model.rs:390-421,1418-1740), up to 512 activation rows in
+// ONE pass over the weights.
+//
+//   y[M,N] = x[M,K] @ W[N,K]^T,  W in GGUF Q8_0 / Q4_K blocks, x and y f32.
+//
+// The contraction runs over the BYTE STREAM of a weight row, not over k. A CTA owns 128 weight
+// rows; one elected thread pulls boxes of 128 rows x 128 bytes of the block matrix
+// [N][row_bytes] into a ring of shared-memory slots with 2-D tensor-map copies (128-byte
+// swizzle, so that 16-byte reads with one lane per row are free of bank conflicts; rows and
+// bytes past the matrix are zero-filled by the copy engine). A box does not line up with the
+// 34-byte (Q8_0) or 144-byte (Q4_K) blocks and it does not have to: the sum over k may be taken
+// in any order as long as both operands agree, so every 16-byte chunk of the stream becomes MMA
+// k-positions in the order its bytes lie in memory, and a small pack kernel lays the
+// activations out in that same order (zero at the positions of scale bytes and headers):
+//   * Q8_0: one chunk = 16 positions = one k-step; a position that holds a byte of a block's
+//     f16 scale is multiplied by a zero on the activation side. No realignment of the 2-byte-
+//     aligned int8 runs is ever done.
+//   * Q4_K: one nibble chunk = 16 low nibbles + 16 high nibbles = two k-steps (sub-blocks 2g
+//     and 2g+1 of the chunk's 64-weight group); header chunks produce nothing and are skipped
+//     by the MMA issuer.
+// 16 producer warps (thread = weight row x chunk) read the raw chunks, dequantise with packed
+// f16 arithmetic (Q8_0: exact int8 -> f16 by byte permute, one rounding in d*q; Q4_K:
+// d*sc*(q-8) - (dmin*m - 8*d*sc) with both factors rounded once to f16) and store 16-byte
+// core-matrix rows of the A tile (K-major, no swizzle). One warp issues tcgen05.mma
+// (kind::f16, M = 128 weight rows, N = up to 256 activation rows per instruction, f32
+// accumulation in up to 512 TMEM columns); one warp streams the packed activations through a
+// ring of bulk copies. All hand-offs are mbarriers with bounded waits: a wait that runs out sets
+// the status word, the CTA drains its own copies, frees its TMEM and returns.
+//
+// Numerics: both operands are rounded once to f16 (as the f16 tensor path prescribes); the
+// products are exact and accumulate in f32. The error of a K = 4096 product is about 1e-4 of
+// the output scale against the 1e-3 bound. The decode step's chain of matmuls keeps the
+// three-product kernel in gemm_tc.cu.
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up through the runtime
+
+#include <mutex>
+
+#include "ctx.h"
+#include "tc05.cuh"
+
+namespace kanso {
+
+constexpr int TM_PRODUCERS = 512;              // 16 warps: dequantise, then run the epilogue
+constexpr int TM_THREADS = TM_PRODUCERS + 96;  // + MMA issuer, weight loader, activation loader
+constexpr int TM_TILE_N = 128;                 // weight rows per CTA = MMA M
+constexpr int TM_BOX_W = 128;                  // bytes of a weight row per box (the swizzle span)
+constexpr int TM_BOX = TM_TILE_N * TM_BOX_W;   // 16 KB per ring slot
+constexpr int TM_RAW_SLOTS = 5;
+constexpr int TM_A_STAGE = 32768;  // 16 k-chunks of 8 positions x 128 rows x 16 bytes
+constexpr int TM_B_SLOTS = 4;
+constexpr int TM_FMT_Q8_0 = 0;
+constexpr int TM_FMT_Q4_K = 1;
+constexpr int TM_MAX_M = 512;
+
+struct TmArgs {
+  float* y;            // [M, N]
+  const uint8_t* bp;   // packed activations: units of [2 k-chunks][Mt rows][8 f16]
+  int64_t N;
+  int M, Mt;           // Mt = M rounded up to 16
+  int row_bytes;       // bytes of one weight row
+  int boxes_total;     // ceil(row_bytes / 128)
+  int ksplit;          // CTAs along the stream; > 1: partial sums are added into y with atomics
+  int ub;              // activation units per ring slot (1, 2 or 4)
+  int* status;
+};
+
+// Result buffer the pack kernel clears on the way (a split launch adds into it).
+struct TmZero {
+  float* p;
+  int64_t n;
+};
+
+// The k index a stream position stands for, or -1 where the byte is not a weight.
+// Q8_0: chunk `gc` of the row stream, byte j of it.
+__device__ __forceinline__ int tm_k_of_q8_0(int gc, int j) {
+  const int o = 16 * gc + j;
+  const int blk = o / 34, within = o - 34 * blk;
+  return within >= 2 ? 32 * blk + within - 2 : -1;
+}
+// Q4_K: nibble chunk; hs = 0 low nibbles, 1 high nibbles; q = position 0..15 inside the k-step.
+// Inside a 32-bit word the positions run over bytes 0, 2, 1, 3: that is how the masked half2
+// pairs fall out of the word in the producer.
+__device__ __forceinline__ int tm_k_of_q4_k(int gc, int hs, int q) {
+  const int o = 16 * gc;
+  const int sb = o / 144, rem = o - 144 * sb;
+  if (rem == 0) return -1;  // header chunk
+  const int i = (rem >> 4) - 1;
+  const int r = q & 3;
+  const int byte = 4 * (q >> 2) + (r == 0 ? 0 : r == 1 ? 2 : r == 2 ? 1 : 3);
+  const int nb = 16 * i + byte;
+  return 256 * sb + 64 * (nb >> 5) + (nb & 31) + 32 * hs;
+}
+
+// x f32 [M,K] -> f16 in stream order. One thread per (unit, k-chunk of 8, row): 16 bytes.
+template <int FMT>
+__global__ void tm_pack_kernel(const float* __restrict__ x, __half* __restrict__ bp, int M, int Mt,
+                               int K, int units_total, const TmZero zero) {
+  pdl_launch_dependents();
+  pdl_wait();  // x (and the readers of the buffer cleared here) belong to earlier kernels
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t j = gtid; j < zero.n; j += nthreads) zero.p[j] = 0.f;
+  const int64_t total = (int64_t)units_total * 2 * Mt;
+  for (int64_t i = gtid; i < total; i += nthreads) {
+    const int m = (int)(i % Mt);
+    const int uk = (int)(i / Mt);  // unit * 2 + k-chunk
+    const int u = uk >> 1, kc8 = uk & 1;
+    __align__(16) __half v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int k;
+      if (FMT == TM_FMT_Q8_0)
+        k = tm_k_of_q8_0(u, 8 * kc8 + e);
+      else
+        k = tm_k_of_q4_k(u >> 1, u & 1, 8 * kc8 + e);
+      const float f = (m < M && k >= 0 && k < K) ? x[(int64_t)m * K + k] : 0.f;
+      v[e] = __float2half_rn(f);
+    }
+    *reinterpret_cast<uint4*>(bp + i * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];" ::"r"(smem_u32(dst_smem)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Address of 16-byte chunk `chunk` of row `row` inside a swizzled box.
+__device__ __forceinline__ const uint8_t* tm_chunk(const uint8_t* slot, int row, int chunk) {
+  return slot + row * TM_BOX_W + ((chunk ^ (row & 7)) << 4);
+}
+
+// Q8_0: this thread's chunk (16 stream bytes of its row) -> 16 f16 values d*q in the A tile.
+// `idx` counts boxes from the first one this CTA loaded (ring position), `box` is the box's
+// index in the row stream. A block's scale always precedes its values in the stream, at most
+// 33 bytes back: in this box or in the one before it, which is still in the ring.
+__device__ __forceinline__ void tm_dequant_q8_0(const uint8_t* Raw, int idx, int box, int cib,
+                                                int c, int row, uint8_t* Ab) {
+  const uint8_t* slot = Raw + (idx % TM_RAW_SLOTS) * TM_BOX;
+  const uint4 v = *reinterpret_cast<const uint4*>(tm_chunk(slot, row, cib));
+  const uint32_t o = (uint32_t)box * TM_BOX_W + (uint32_t)cib * 16u;  // warp-uniform
+  const uint32_t blk = o / 34u, within0 = o - 34u * blk;              // within0 is even
+  // byte pairs [0, s) of the chunk lie in block blk, pair s (if any) is the scale of block
+  // blk + 1, the pairs after it are that block's values
+  const uint32_t s = min(8u, (34u - within0) >> 1);
+  __half2 da = __float2half2_rn(0.f), db = da;
+  if (within0 != 0) {  // the scale of block blk sits before this chunk
+    const uint32_t od = 34u * blk, bd = od >> 7, in_box = od & 127u;
+    const uint8_t* sd = Raw + ((idx - (int)((uint32_t)box - bd)) % TM_RAW_SLOTS) * TM_BOX;
+    da = __half2half2(*reinterpret_cast<const __half*>(tm_chunk(sd, row, in_box >> 4) +
+                                                       (in_box & 15u)));
+  }
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (within0 == 0) {  // pair 0 is the scale of block blk itself
+    da = __half2half2(__ushort_as_half((unsigned short)(v.x & 0xFFFFu)));
+  } else if (s < 8) {
+    const uint32_t si = s >> 1;
+    const uint32_t ws = si == 0 ? v.x : si == 1 ? v.y : si == 2 ? v.z : v.w;
+    db = __half2half2(__ushort_as_half((unsigned short)((s & 1) ? (ws >> 16) : (ws & 0xFFFFu))));
+  }
+  const __half2 zero2 = __float2half2_rn(0.f);
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128, exact in f16
+  uint32_t out[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t q = w[i] ^ 0x80808080u;
+    // 0x6400 | byte = 1024 + (q + 128) as f16, exactly
+    const __half2 q01 = __hsub2(u32_as_h2(__byte_perm(q, 0x64646464u, 0x4140)), bias);
+    const __half2 q23 = __hsub2(u32_as_h2(__byte_perm(q, 0x64646464u, 0x4342)), bias);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t p = 2 * i + h;  // byte pair of the chunk
+      __half2 d2;
+      if (p < s)
+        d2 = (p == 0 && within0 == 0) ? zero2 : da;  // a scale's own bytes count as zero
+      else
+        d2 = p == s ? zero2 : db;
+      out[p] = h2_as_u32(__hmul2(h ? q23 : q01, d2));
+    }
+  }
+  uint8_t* dst = Ab + (2 * c) * (TM_TILE_N * 16) + row * 16;
+  *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
+  *reinterpret_cast<uint4*>(dst + TM_TILE_N * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
+// Q4_K: this thread's nibble chunk -> two k-steps of 16 f16 values (low nibbles = sub-block 2g,
+// high nibbles = sub-block 2g+1 of the chunk's 64-weight group). w = d1*(q-8) - (m1 - 8*d1) with
+// d1 = d*sc, m1 = dmin*m (src/quant/q4_k.rs:30-55): centred on 8 so that the two f16 factors
+// carry a small constant instead of one the size of the weight range.
+__device__ __forceinline__ void tm_dequant_q4_k(const uint8_t* Raw, int idx, int box, int cib,
+                                                int c, int row, uint8_t* Ab) {
+  const uint32_t o = (uint32_t)box * TM_BOX_W + (uint32_t)cib * 16u;  // warp-uniform
+  const uint32_t sb = o / 144u, rem = o - 144u * sb;
+  if (rem == 0) return;  // header chunk: the MMA issuer skips its two k-steps
+  const uint32_t i = (rem >> 4) - 1u;
+  const uint8_t* slot = Raw + (idx % TM_RAW_SLOTS) * TM_BOX;
+  const uint4 qv = *reinterpret_cast<const uint4*>(tm_chunk(slot, row, cib));
+  // the super-block's header: at most 128 bytes back, in this box or the one before it
+  const uint32_t oh = 144u * sb, bh = oh >> 7;
+  const uint8_t* sh = Raw + ((idx - (int)((uint32_t)box - bh)) % TM_RAW_SLOTS) * TM_BOX;
+  const uint4 hdr = *reinterpret_cast<const uint4*>(tm_chunk(sh, row, (oh & 127u) >> 4));
+  const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+  uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+  unpack_scales_k4(hdr.y, hdr.z, hdr.w, sc_lo, sc_hi, mn_lo, mn_hi);
+  const uint32_t g = i >> 1;  // 64-weight group; sub-blocks 2g (low) and 2g+1 (high)
+  const uint32_t scw = g < 2 ? sc_lo : sc_hi, mnw = g < 2 ? mn_lo : mn_hi;
+  const uint32_t sh0 = 16u * (g & 1u);
+  const float d1l = d * (float)((scw >> sh0) & 0xFFu), d1h = d * (float)((scw >> (sh0 + 8)) & 0xFFu);
+  const float m1l = dmin * (float)((mnw >> sh0) & 0xFFu);
+  const float m1h = dmin * (float)((mnw >> (sh0 + 8)) & 0xFFu);
+  const __half2 dl2 = __float2half2_rn(d1l), dh2 = __float2half2_rn(d1h);
+  const __half2 cl2 = __float2half2_rn(8.0f * d1l - m1l), ch2 = __float2half2_rn(8.0f * d1h - m1h);
+  const __half2 bias = __floats2half2_rn(1032.f, 1032.f);  // 1024 + 8
+  const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    // 0x6400 | nibble = 1024 + q as f16; pairs (byte 0, byte 2) and (byte 1, byte 3)
+    const uint32_t t0 = (w[k] & 0x000F000Fu) | 0x64006400u;
+    const uint32_t t1 = ((w[k] >> 4) & 0x000F000Fu) | 0x64006400u;
+    const uint32_t t2 = ((w[k] >> 8) & 0x000F000Fu) | 0x64006400u;
+    const uint32_t t3 = ((w[k] >> 12) & 0x000F000Fu) | 0x64006400u;
+    lo[2 * k] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t0), bias), dl2, cl2));
+    lo[2 * k + 1] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t2), bias), dl2, cl2));
+    hi[2 * k] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t1), bias), dh2, ch2));
+    hi[2 * k + 1] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t3), bias), dh2, ch2));
+  }
+  uint8_t* dst = Ab + (4 * c) * (TM_TILE_N * 16) + row * 16;  // k-steps 2c (low) and 2c+1 (high)
+  *reinterpret_cast<uint4*>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  *reinterpret_cast<uint4*>(dst + TM_TILE_N * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+  *reinterpret_cast<uint4*>(dst + 2 * TM_TILE_N * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  *reinterpret_cast<uint4*>(dst + 3 * TM_TILE_N * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TM_THREADS, 1)
+    gemm_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int UPC = FMT == TM_FMT_Q8_0 ? 1 : 2;  // activation units (k-steps) per chunk
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t unit_bytes = 32u * (uint32_t)a.Mt;
+  const uint32_t bslot_bytes = (uint32_t)a.ub * unit_bytes;
+  uint8_t* Raw = smem;
+  uint8_t* As = Raw + TM_RAW_SLOTS * TM_BOX;
+  uint8_t* Bs = As + 2 * TM_A_STAGE;
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(Bs + TM_B_SLOTS * bslot_bytes);
+  uint64_t* raw_empty = raw_full + TM_RAW_SLOTS;
+  uint64_t* a_full = raw_empty + TM_RAW_SLOTS;
+  uint64_t* a_empty = a_full + 2;
+  uint64_t* b_full = a_empty + 2;
+  uint64_t* b_empty = b_full + TM_B_SLOTS;
+  uint64_t* acc_full = b_empty + TM_B_SLOTS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int n0 = (int)blockIdx.x * TM_TILE_N;
+  const int b0 = (int)((int64_t)a.boxes_total * blockIdx.y / a.ksplit);
+  const int b1 = (int)((int64_t)a.boxes_total * (blockIdx.y + 1) / a.ksplit);
+  // a chunk at the start of this CTA's range may need a scale or header from the box before it
+  const int first = b0 > 0 ? b0 - 1 : 0;
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)a.Mt) ncols <<= 1;
+
+  if (warp == 0) tmem_alloc(tmem_slot, ncols);
+  if (tid == 32) {
+    for (int i = 0; i < TM_RAW_SLOTS; ++i) {
+      mbar_init(&raw_full[i], 1);
+      mbar_init(&raw_empty[i], TM_PRODUCERS / 32);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&a_full[i], TM_PRODUCERS / 32);
+      mbar_init(&a_empty[i], 1);
+    }
+    for (int i = 0; i < TM_B_SLOTS; ++i) {
+      mbar_init(&b_full[i], 1);
+      mbar_init(&b_empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // The weights never depend on the kernel before this one (the activation pack): their boxes
+  // are requested at once; the activation loader waits for the pack.
+  pdl_launch_dependents();
+
+  if (warp < TM_PRODUCERS / 32) {
+    const int row = tid & 127, c = tid >> 7;  // c: chunk of the sub-stage, warp-uniform
+    int abuf = 0;
+    uint32_t a_par = 1;  // parity that an unused a_empty barrier already satisfies
+    for (int box = first, idx = 0; box < b1; ++box, ++idx) {
+      if (!mbar_wait_bounded(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u))
+        *abort_flag = 1;
+      if (*abort_flag) break;
+      if (box >= b0) {
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          if (!mbar_wait_bounded(&a_empty[abuf], a_par)) *abort_flag = 1;
+          if (*abort_flag) break;
+          uint8_t* Ab = As + abuf * TM_A_STAGE;
+          if (FMT == TM_FMT_Q8_0)
+            tm_dequant_q8_0(Raw, idx, box, half * 4 + c, c, row, Ab);
+          else
+            tm_dequant_q4_k(Raw, idx, box, half * 4 + c, c, row, Ab);
+          fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[abuf]);
+          abuf ^= 1;
+          if (abuf == 0) a_par ^= 1u;
+        }
+      }
+      // the box before this one is no longer needed (scales and headers reach one box back)
+      __syncwarp();
+      if (idx >= 1 && lane == 0) mbar_arrive(&raw_empty[(idx - 1) % TM_RAW_SLOTS]);
+    }
+  } else if (warp == TM_PRODUCERS / 32) {
+    // ---- MMA issuer: one thread, and every instruction it executes sits on the critical
+    // path of the whole CTA, so the loop carries running descriptors and counters: no
+    // division, no address rebuilt from scratch ----
+    if (lane == 0) {
+      const bool two = a.Mt > 256;  // a second accumulator chunk of columns 256..
+      const uint32_t idesc0 = tc_idesc_f16(TM_TILE_N, two ? 256 : a.Mt);
+      const uint32_t idesc1 = tc_idesc_f16(TM_TILE_N, two ? a.Mt - 256 : 16);
+      const uint64_t adesc_buf0 = tc_smem_desc(smem_u32(As), TM_TILE_N * 16, 128);
+      const uint64_t bdesc_base = tc_smem_desc(smem_u32(Bs), (uint32_t)a.Mt * 16u, 128);
+      const uint32_t a_kstep = (2u * (TM_TILE_N * 16)) >> 4;  // descriptor units per k-step of A
+      const uint32_t b_unit = unit_bytes >> 4, b_slot = bslot_bytes >> 4;
+      const uint32_t ub = (uint32_t)a.ub, row_bytes = (uint32_t)a.row_bytes;
+      uint32_t o = (uint32_t)b0 * TM_BOX_W;      // stream offset of the next chunk
+      uint32_t cm = ((uint32_t)b0 * 8u) % 9u;    // Q4_K: chunk index modulo 9, 0 = header
+      uint32_t bslot = 0, b_par = 0, in_grp = 0, acc = 0;
+      uint64_t bdesc = bdesc_base;
+      int abuf = 0;
+      uint32_t a_par = 0;
+      bool ok = true;
+      for (int ss = 2 * (b1 - b0); ss > 0 && ok; --ss) {
+        if (!mbar_wait_bounded(&a_full[abuf], a_par)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint64_t adesc = adesc_buf0 + (uint64_t)((uint32_t)abuf * (TM_A_STAGE >> 4));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const bool valid = o < row_bytes && (FMT == TM_FMT_Q8_0 || cm != 0);
+#pragma unroll
+          for (int ks = 0; ks < UPC; ++ks) {
+            if (in_grp == 0) {
+              if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
+              tc_fence_after();
+              bdesc = bdesc_base + (uint64_t)(bslot * b_slot);
+            }
+            if (valid && ok) {
+              tc_mma_f16(tmem_base, adesc, bdesc, idesc0, acc);
+              if (two) tc_mma_f16(tmem_base + 256u, adesc, bdesc + 256u, idesc1, acc);
+              acc = 1;
+            }
+            adesc += a_kstep;
+            bdesc += b_unit;
+            if (++in_grp == ub) {
+              tc_commit(&b_empty[bslot]);
+              in_grp = 0;
+              if (++bslot == TM_B_SLOTS) {
+                bslot = 0;
+                b_par ^= 1u;
+              }
+            }
+          }
+          o += 16u;
+          if (FMT == TM_FMT_Q4_K) cm = cm == 8u ? 0u : cm + 1u;
+        }
+        tc_commit(&a_empty[abuf]);
+        abuf ^= 1;
+        if (abuf == 0) a_par ^= 1u;
+      }
+      if (ok)
+        tc_commit(acc_full);
+      else
+        *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == TM_PRODUCERS / 32 + 1) {
+    // ---- weight loader: one box per ring slot, as far ahead as the ring allows ----
+    if (lane == 0) {
+      int issued = 0;
+      for (int box = first, idx = 0; box < b1; ++box, ++idx) {
+        const int slot = idx % TM_RAW_SLOTS;
+        if (!mbar_wait_bounded(&raw_empty[slot], ((uint32_t)(idx / TM_RAW_SLOTS) & 1u) ^ 1u) ||
+            *abort_flag) {
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(&raw_full[slot], TM_BOX);
+        tma_load_2d(Raw + slot * TM_BOX, &tmap, box * TM_BOX_W, n0, &raw_full[slot]);
+        issued = idx + 1;
+      }
+      // leave only when every copy this thread started has landed (bounded)
+      for (int idx = max(0, issued - TM_RAW_SLOTS); idx < issued; ++idx)
+        mbar_wait_bounded(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u);
+    }
+    __syncwarp();
+  } else {
+    // ---- activation loader: ring slots of `ub` units, contiguous in the packed buffer ----
+    if (lane == 0) {
+      pdl_wait();  // the pack kernel has written the activations
+      const uint32_t g0 = (uint32_t)b0 * 8u * UPC / (uint32_t)a.ub;
+      const uint32_t g1 = (uint32_t)b1 * 8u * UPC / (uint32_t)a.ub;
+      uint32_t issued = 0;
+      for (uint32_t g = g0; g < g1; ++g) {
+        const uint32_t l = g - g0, slot = l % TM_B_SLOTS;
+        if (!mbar_wait_bounded(&b_empty[slot], ((l / TM_B_SLOTS) & 1u) ^ 1u) || *abort_flag) {
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(&b_full[slot], bslot_bytes);
+        bulk_g2s(Bs + slot * bslot_bytes, a.bp + (size_t)g * bslot_bytes, bslot_bytes,
+                 &b_full[slot]);
+        issued = l + 1;
+      }
+      for (uint32_t l = issued > TM_B_SLOTS ? issued - TM_B_SLOTS : 0; l < issued; ++l)
+        mbar_wait_bounded(&b_full[l % TM_B_SLOTS], (l / TM_B_SLOTS) & 1u);
+    }
+    __syncwarp();
+  }
+
+  __syncthreads();
+  int failed = *abort_flag != 0;
+  if (!failed) failed = !mbar_wait_bounded(acc_full, 0);
+  failed = __syncthreads_or(failed);
+  tc_fence_after();
+  pdl_wait();  // y (cleared by the pack kernel of a split launch) belongs to the kernel before
+  if (!failed && warp < TM_PRODUCERS / 32) {
+    // lane = weight row inside the tile, TMEM column = activation row
+    const int q = warp & 3;
+    const int64_t n = (int64_t)n0 + q * 32 + lane;
+    for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TM_PRODUCERS / 128) {
+      uint32_t r[16];
+      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
+      if (n < a.N) {
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          const int m = c16 * 16 + jj;
+          if (m < a.M) {
+            float* dst = a.y + (int64_t)m * a.N + n;
+            if (a.ksplit == 1)
+              *dst = __uint_as_float(r[jj]);
+            else
+              atomicAdd(dst, __uint_as_float(r[jj]));  // y was cleared by the pack kernel
+          }
+        }
+      }
+    }
+  } else if (failed && tid == 0) {
+    atomicOr(a.status, DEV_WAIT_TIMEOUT);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, ncols);
+}
+
+// cuTensorMapEncodeTiled, looked up once through the runtime (no link-time dependency on the
+// driver library).
+typedef CUresult (*TmEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmEncodeFn tm_encoder() {
+  static std::once_flag once;
+  static TmEncodeFn fn = nullptr;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TmEncodeFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// y[M,N] = x[M,K] @ W^T for 9..512 activation rows. Sets *handled = false (and launches
+// nothing) when the shape is outside this kernel's range: rows of the block matrix must start
+// on 16-byte boundaries (every Q4_K matrix; Q8_0 when K % 256 == 0).
+int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
+                   int64_t M, int64_t N, int64_t K, bool* handled) {
+  *handled = false;
+  if (dtype != KANSO_DTYPE_Q8_0 && dtype != KANSO_DTYPE_Q4_K) return KANSO_OK;
+  const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
+  const int bb = dtype == KANSO_DTYPE_Q8_0 ? Q8_BYTES : Q4K_BYTES;
+  if (M < 9 || M > TM_MAX_M || N < 1 || K < blk || K % blk != 0 || !w || !x || !y) return KANSO_OK;
+  const int64_t row_bytes = K / blk * bb;
+  if (row_bytes % 16 != 0 || !aligned16(w) || row_bytes > (1 << 28) || N > (1 << 30))
+    return KANSO_OK;
+  TmEncodeFn encode = tm_encoder();
+  if (!encode) return KANSO_OK;
+
+  const int Mt = (int)((M + 15) / 16 * 16);
+  const int boxes_total = (int)((row_bytes + TM_BOX_W - 1) / TM_BOX_W);
+  const int upc = dtype == KANSO_DTYPE_Q8_0 ? 1 : 2;
+  const int units_total = boxes_total * 8 * upc;
+  const int tiles_n = (int)((N + TM_TILE_N - 1) / TM_TILE_N);
+  // Split the stream while the grid stays within about one wave of CTAs (one CTA per SM) and
+  // every CTA keeps at least four boxes; the partial sums of a split are added with atomics
+  // onto a y that the pack kernel clears.
+  int ksplit = 1;
+  while (tiles_n * ksplit * 2 <= ctx->sm_count + ctx->sm_count / 4 &&
+         boxes_total / (ksplit * 2) >= 4)
+    ksplit *= 2;
+  // activation units per ring slot: a whole sub-stage (4 chunks) when that stays at or below
+  // 16 KB, else the largest power-of-two share of it that does
+  int ub = 1;
+  while (ub * 2 <= 4 * upc && ub * 2 * 32 * Mt <= 16384) ub *= 2;
+
+  CUtensorMap tmap;
+  const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
+  const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {TM_BOX_W, TM_TILE_N};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), gdim,
+                             gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS)
+    return fail(ctx, KANSO_ERR_DEVICE, "gemm_tma: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+
+  const size_t bp_bytes = (size_t)units_total * 32 * Mt;
+  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, bp_bytes + 256);
+  if (!scratch) return KANSO_ERR_DEVICE;
+  *handled = true;
+
+  TmZero zero = {nullptr, 0};
+  if (ksplit > 1) {
+    zero.p = y;
+    zero.n = M * N;
+  }
+  const int64_t pack_items = (int64_t)units_total * 2 * Mt;
+  int64_t pack_blocks = (pack_items + 255) / 256;
+  if (pack_blocks > 8 * ctx->sm_count) pack_blocks = 8 * ctx->sm_count;
+  cudaError_t le;
+  if (dtype == KANSO_DTYPE_Q8_0)
+    le = launch_dependent(ctx, tm_pack_kernel<TM_FMT_Q8_0>, dim3((unsigned)pack_blocks), dim3(256),
+                          0, x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K,
+                          units_total, zero);
+  else
+    le = launch_dependent(ctx, tm_pack_kernel<TM_FMT_Q4_K>, dim3((unsigned)pack_blocks), dim3(256),
+                          0, x, reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K,
+                          units_total, zero);
+  if (le != cudaSuccess) return cuda_fail(ctx, le, "gemm_tma pack launch");
+  int32_t st = after_launch(ctx, "gemm_tma pack activations");
+  if (st) return st;
+
+  TmArgs a;
+  a.y = y;
+  a.bp = scratch;
+  a.N = N;
+  a.M = (int)M;
+  a.Mt = Mt;
+  a.row_bytes = (int)row_bytes;
+  a.boxes_total = boxes_total;
+  a.ksplit = ksplit;
+  a.ub = ub;
+  a.status = ctx->dev_status;
+  const size_t smem = (size_t)TM_RAW_SLOTS * TM_BOX + 2 * TM_A_STAGE +
+                      (size_t)TM_B_SLOTS * ub * 32 * Mt + 256;
+  if (smem > (size_t)ctx->smem_optin)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED, "gemm_tma: %zu bytes of shared memory needed", smem);
+  auto kern = dtype == KANSO_DTYPE_Q8_0 ? gemm_tma_kernel<TM_FMT_Q8_0> : gemm_tma_kernel<TM_FMT_Q4_K>;
+  static bool attr_set[2][16] = {};
+  bool& done = attr_set[dtype == KANSO_DTYPE_Q8_0 ? 0 : 1][ctx->device & 15];
+  if (!done) {
+    KANSO_CUDA_TRY(ctx,
+                   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ctx->smem_optin),
+                   "gemm_tma: shared memory opt-in");
+    done = true;
+  }
+  le = launch_dependent(ctx, kern, dim3(tiles_n, ksplit), dim3(TM_THREADS), smem, tmap, a);
+  if (le != cudaSuccess) return cuda_fail(ctx, le, "gemm_tma launch");
+  return after_launch(ctx, "gemm_tma");
+}
+
+}  // namespace kanso

@@ -16,8 +16,27 @@ int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float
                       float eps, const float* resid, int64_t K, int M, int32_t act_mode,
                       bool decode_chain, bool* handled);
 
+int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
+                   int64_t M, int64_t N, int64_t K, bool* handled);
+
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
+  // More than 8 activation rows on a matrix whose rows start on 16-byte boundaries: the
+  // TMA-staged tcgen05 GEMM, up to 512 rows per pass over the weights.
+  if (M > 8 && act_mode == KANSO_ACT_F32 && N > 0 && K > 0 && w && x && y) {
+    bool all = true;
+    for (int64_t m0 = 0; m0 < M && all; m0 += 512) {
+      bool handled = false;
+      // a tail of fewer than 9 rows rides with the chunk before it
+      int64_t mc = M - m0 < 512 ? M - m0 : 512;
+      if (M - m0 - mc > 0 && M - m0 - mc < 9) mc -= 16;
+      int32_t st = tma_matmul(ctx, dtype, w, x + m0 * K, y + m0 * N, mc, N, K, &handled);
+      if (st != KANSO_OK) return st;
+      if (!handled) all = false;
+      m0 -= 512 - mc;
+    }
+    if (all) return KANSO_OK;
+  }
   // More than 8 activation rows: the tcgen05 GEMM, at most 128 rows per pass over the weights
   // (the A/B tiles of two stages plus the raw-byte ring fill one SM's shared memory).
   if (M > 8 && act_mode == KANSO_ACT_F32 && (dtype == KANSO_DTYPE_Q8_0 || dtype == KANSO_DTYPE_Q4_K) &&
