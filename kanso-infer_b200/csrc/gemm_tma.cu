@@ -43,7 +43,7 @@
 namespace kanso {
 
 constexpr int TM_PRODUCERS = 512;              // 16 warps: dequantise, then run the epilogue
-constexpr int TM_THREADS = TM_PRODUCERS + 96;  // + MMA issuer, weight loader, activation loader
+constexpr int TM_THREADS = 768;  // 24 warps: scheduler 0 holds the MMA issuer and the two loaders
 constexpr int TM_TILE_N = 128;                 // weight rows per CTA = MMA M
 constexpr int TM_BOX_W = 128;                  // bytes of a weight row per box (the swizzle span)
 constexpr int TM_BOX = TM_TILE_N * TM_BOX_W;   // 16 KB per ring slot
@@ -53,6 +53,9 @@ constexpr int TM_B_SLOTS = 4;
 constexpr int TM_FMT_Q8_0 = 0;
 constexpr int TM_FMT_Q4_K = 1;
 constexpr int TM_MAX_M = 512;
+#ifndef TM_POLL_NS
+#define TM_POLL_NS 20
+#endif
 
 struct TmArgs {
   float* y;            // [M, N]
@@ -62,7 +65,7 @@ struct TmArgs {
   int row_bytes;       // bytes of one weight row
   int boxes_total;     // ceil(row_bytes / 128)
   int ksplit;          // CTAs along the stream; > 1: partial sums are added into y with atomics
-  int ub;              // activation units per ring slot (1, 2 or 4)
+  int ub;              // activation units per ring slot (1, 2, 4 or 8)
   int* status;
 };
 
@@ -241,12 +244,45 @@ __device__ __forceinline__ void tm_dequant_q4_k(const uint8_t* Raw, int idx, int
   *reinterpret_cast<uint4*>(dst + 3 * TM_TILE_N * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
 }
 
+// One warp-wide wait with a single poller: lane 0 watches the barrier, the other lanes meet it at
+// the warp barrier (16 pollers per CTA instead of 512 on one shared-memory word).
+// Bounded wait for the roles that are NOT the MMA issuer: between polls the thread sleeps, so
+// that its polling does not crowd the issuer's own barrier and tensor-core instructions out of
+// the SM's shared-memory instruction queue.
+__device__ __forceinline__ bool tm_wait_polite(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 21); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(TM_POLL_NS);
+  }
+  return false;
+}
+__device__ __forceinline__ bool tm_warp_wait(uint64_t* bar, uint32_t parity, int lane) {
+  bool ok = true;
+  if (lane == 0) ok = tm_wait_polite(bar, parity);
+  return __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0;
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(TM_THREADS, 1)
     gemm_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int UPC = FMT == TM_FMT_Q8_0 ? 1 : 2;  // activation units (k-steps) per chunk
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Chunks per A stage: both formats fill a 32 KB stage (Q8_0: a whole box, Q4_K: half a box).
+  // Every hand-off between the roles costs a few hundred cycles, so stages are as large as the
+  // shared memory allows.
+  constexpr int CH = FMT == TM_FMT_Q8_0 ? 8 : 4;
+  constexpr int SPB = 8 / CH;  // stages per box
+  // Warp w runs on warp scheduler w % 4. Every instruction of the MMA issuer is on the CTA's
+  // critical path, so scheduler 0 carries only that warp and the two loaders (one thread each,
+  // mostly asleep on a barrier); the 16 dequantising warps sit on schedulers 1..3.
+  const int pw = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int warp;  // role: 0..15 producer, 16 MMA issuer, 17 weight loader, 18 activation loader, 19 none
+  if ((pw & 3) == 0)
+    warp = (pw >> 2) < 3 ? 16 + (pw >> 2) : 19;
+  else
+    warp = (pw & 3) - 1 + 3 * (pw >> 2);
+  if (warp >= 16 && (pw & 3) != 0) warp = 19;
+  const int tid = warp * 32 + lane;
   const uint32_t unit_bytes = 32u * (uint32_t)a.Mt;
   const uint32_t bslot_bytes = (uint32_t)a.ub * unit_bytes;
   uint8_t* Raw = smem;
@@ -270,8 +306,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
   uint32_t ncols = 32;
   while (ncols < (uint32_t)a.Mt) ncols <<= 1;
 
-  if (warp == 0) tmem_alloc(tmem_slot, ncols);
-  if (tid == 32) {
+  if (pw == 0) tmem_alloc(tmem_slot, ncols);
+  if (threadIdx.x == 32) {
     for (int i = 0; i < TM_RAW_SLOTS; ++i) {
       mbar_init(&raw_full[i], 1);
       mbar_init(&raw_empty[i], TM_PRODUCERS / 32);
@@ -297,23 +333,27 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
   pdl_launch_dependents();
 
   if (warp < TM_PRODUCERS / 32) {
-    const int row = tid & 127, c = tid >> 7;  // c: chunk of the sub-stage, warp-uniform
+    const int row = tid & 127, c = tid >> 7;  // c: chunk within a group of four, warp-uniform
     int abuf = 0;
     uint32_t a_par = 1;  // parity that an unused a_empty barrier already satisfies
     for (int box = first, idx = 0; box < b1; ++box, ++idx) {
-      if (!mbar_wait_bounded(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u))
+      if (!tm_warp_wait(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u, lane))
         *abort_flag = 1;
       if (*abort_flag) break;
       if (box >= b0) {
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          if (!mbar_wait_bounded(&a_empty[abuf], a_par)) *abort_flag = 1;
+        for (int st = 0; st < SPB; ++st) {
+          if (!tm_warp_wait(&a_empty[abuf], a_par, lane)) *abort_flag = 1;
           if (*abort_flag) break;
           uint8_t* Ab = As + abuf * TM_A_STAGE;
-          if (FMT == TM_FMT_Q8_0)
-            tm_dequant_q8_0(Raw, idx, box, half * 4 + c, c, row, Ab);
-          else
-            tm_dequant_q4_k(Raw, idx, box, half * 4 + c, c, row, Ab);
+#pragma unroll
+          for (int j = 0; j < CH / 4; ++j) {
+            const int kc = 4 * j + c;  // chunk of the stage
+            if (FMT == TM_FMT_Q8_0)
+              tm_dequant_q8_0(Raw, idx, box, st * CH + kc, kc, row, Ab);
+            else
+              tm_dequant_q4_k(Raw, idx, box, st * CH + kc, kc, row, Ab);
+          }
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
           __syncwarp();
           if (lane == 0) mbar_arrive(&a_full[abuf]);
@@ -345,7 +385,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       int abuf = 0;
       uint32_t a_par = 0;
       bool ok = true;
-      for (int ss = 2 * (b1 - b0); ss > 0 && ok; --ss) {
+      for (int ss = SPB * (b1 - b0); ss > 0 && ok; --ss) {
         if (!mbar_wait_bounded(&a_full[abuf], a_par)) {
           ok = false;
           break;
@@ -353,7 +393,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
         tc_fence_after();
         uint64_t adesc = adesc_buf0 + (uint64_t)((uint32_t)abuf * (TM_A_STAGE >> 4));
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CH; ++c) {
           const bool valid = o < row_bytes && (FMT == TM_FMT_Q8_0 || cm != 0);
 #pragma unroll
           for (int ks = 0; ks < UPC; ++ks) {
@@ -397,7 +437,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       int issued = 0;
       for (int box = first, idx = 0; box < b1; ++box, ++idx) {
         const int slot = idx % TM_RAW_SLOTS;
-        if (!mbar_wait_bounded(&raw_empty[slot], ((uint32_t)(idx / TM_RAW_SLOTS) & 1u) ^ 1u) ||
+        if (!tm_wait_polite(&raw_empty[slot], ((uint32_t)(idx / TM_RAW_SLOTS) & 1u) ^ 1u) ||
             *abort_flag) {
           *abort_flag = 1;
           break;
@@ -408,10 +448,10 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       }
       // leave only when every copy this thread started has landed (bounded)
       for (int idx = max(0, issued - TM_RAW_SLOTS); idx < issued; ++idx)
-        mbar_wait_bounded(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u);
+        tm_wait_polite(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u);
     }
     __syncwarp();
-  } else {
+  } else if (warp == TM_PRODUCERS / 32 + 2) {
     // ---- activation loader: ring slots of `ub` units, contiguous in the packed buffer ----
     if (lane == 0) {
       pdl_wait();  // the pack kernel has written the activations
@@ -420,7 +460,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       uint32_t issued = 0;
       for (uint32_t g = g0; g < g1; ++g) {
         const uint32_t l = g - g0, slot = l % TM_B_SLOTS;
-        if (!mbar_wait_bounded(&b_empty[slot], ((l / TM_B_SLOTS) & 1u) ^ 1u) || *abort_flag) {
+        if (!tm_wait_polite(&b_empty[slot], ((l / TM_B_SLOTS) & 1u) ^ 1u) || *abort_flag) {
           *abort_flag = 1;
           break;
         }
@@ -430,22 +470,23 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
         issued = l + 1;
       }
       for (uint32_t l = issued > TM_B_SLOTS ? issued - TM_B_SLOTS : 0; l < issued; ++l)
-        mbar_wait_bounded(&b_full[l % TM_B_SLOTS], (l / TM_B_SLOTS) & 1u);
+        tm_wait_polite(&b_full[l % TM_B_SLOTS], (l / TM_B_SLOTS) & 1u);
     }
     __syncwarp();
   }
 
   __syncthreads();
   int failed = *abort_flag != 0;
-  if (!failed) failed = !mbar_wait_bounded(acc_full, 0);
-  failed = __syncthreads_or(failed);
+  if (!failed) failed = !tm_warp_wait(acc_full, 0, lane);
+  failed = __syncthreads_or(failed) ? 1 : 0;
   tc_fence_after();
   pdl_wait();  // y (cleared by the pack kernel of a split launch) belongs to the kernel before
-  if (!failed && warp < TM_PRODUCERS / 32) {
-    // lane = weight row inside the tile, TMEM column = activation row
-    const int q = warp & 3;
+  if (!failed) {
+    // every warp helps: lane = weight row inside the tile (a warp reaches the TMEM lanes of its
+    // own quarter, warp % 4), TMEM column = activation row
+    const int q = pw & 3;
     const int64_t n = (int64_t)n0 + q * 32 + lane;
-    for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TM_PRODUCERS / 128) {
+    for (int c16 = pw >> 2; c16 < a.Mt / 16; c16 += TM_THREADS / 128) {
       uint32_t r[16];
       tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
       if (n < a.N) {
@@ -462,12 +503,12 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
         }
       }
     }
-  } else if (failed && tid == 0) {
+  } else if (failed == 1 && threadIdx.x == 0) {
     atomicOr(a.status, DEV_WAIT_TIMEOUT);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, ncols);
+  if (pw == 0) tmem_dealloc(tmem_base, ncols);
 }
 
 // cuTensorMapEncodeTiled, looked up once through the runtime (no link-time dependency on the
@@ -520,10 +561,10 @@ int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const floa
   while (tiles_n * ksplit * 2 <= ctx->sm_count + ctx->sm_count / 4 &&
          boxes_total / (ksplit * 2) >= 4)
     ksplit *= 2;
-  // activation units per ring slot: a whole sub-stage (4 chunks) when that stays at or below
+  // activation units per ring slot: a whole stage (8 k-steps) when that stays at or below
   // 16 KB, else the largest power-of-two share of it that does
   int ub = 1;
-  while (ub * 2 <= 4 * upc && ub * 2 * 32 * Mt <= 16384) ub *= 2;
+  while (ub * 2 <= 8 && ub * 2 * 32 * Mt <= 16384) ub *= 2;
 
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
