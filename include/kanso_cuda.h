@@ -223,6 +223,60 @@ int32_t kanso_cuda_sum_shards(kanso_cuda_ctx* ctx, const float* parts, int64_t M
  * captured in a CUDA graph. No counterpart in the reference. */
 int32_t kanso_cuda_peer_exchange(kanso_cuda_ctx* ctx, void* const* flags, void* step,
                                  int32_t world, int32_t rank);
+/* NOTE on the three pointer-level calls above (scatter_out / sum_shards / peer_exchange): one
+ * exchange orders the stores of a call against its readers, but it does NOT protect the next
+ * call's stores from a peer that is still reading: a rank one call ahead would overwrite the
+ * buffer under a slower peer. Consecutive calls on the same layer must therefore alternate
+ * between TWO result (or parts) buffers, or be separated by a second exchange placed after the
+ * readers. The sharded-layer objects below do this themselves. */
+
+/* ---- sharded layers as objects: peer-visible memory, the exchange and the forward call, so
+ * that a caller without any Python (Model::linear, src/model.rs:390-397) can shard a layer.
+ * No counterpart in the reference. ---- */
+typedef struct kanso_cuda_shard_group kanso_cuda_shard_group;
+typedef struct kanso_cuda_sharded_linear kanso_cuda_sharded_linear;
+#define KANSO_SHARD_HANDLE_BYTES 64
+#define KANSO_SHARD_ROWS 0 /* output rows split over the ranks; x replicated */
+#define KANSO_SHARD_K 1    /* columns (K) split at block boundaries; partial results summed */
+#define KANSO_SHARD_LOCAL_ONLY 1 /* forward flag, row shard: keep the slice on this rank */
+/* Step 1, every rank: allocates this rank's region of `region_bytes` (the exchange buffers of
+ * all layers created later: 2 * max_m * rows_total * 4 bytes per row-sharded layer,
+ * 2 * max_m * world * rows_total * 4 per K-sharded layer) and writes its 64-byte inter-process
+ * handle to handle_out. world <= 8, all ranks on one node. */
+int32_t kanso_cuda_shard_group_create(kanso_cuda_ctx* ctx, int32_t rank, int32_t world,
+                                      size_t region_bytes, kanso_cuda_shard_group** out,
+                                      void* handle_out);
+/* Step 2: the caller gathers the handles of all ranks (world * 64 bytes, in rank order) over its
+ * own channel and hands them in; the peers' regions are mapped into this process. */
+int32_t kanso_cuda_shard_group_connect(kanso_cuda_shard_group* g, const void* all_handles);
+int32_t kanso_cuda_shard_group_destroy(kanso_cuda_shard_group* g);
+/* LinearWeight::to_device for this rank's shard of an [rows_total x cols_total] weight
+ * (src/weights.rs:140-158). shard_bytes: the blocks of this rank's rows
+ * (kanso_cuda_shard_range(rows_total, rank, world, 8)) for KANSO_SHARD_ROWS, or this rank's
+ * columns re-packed by kanso_cuda_shard_k_repack for KANSO_SHARD_K. Every rank creates the same
+ * layers in the same order (their buffers are found by offset). */
+int32_t kanso_cuda_sharded_linear_create(kanso_cuda_shard_group* g, const void* shard_bytes,
+                                         size_t nbytes, int32_t dtype, int64_t rows_total,
+                                         int64_t cols_total, int32_t mode, int64_t max_m,
+                                         kanso_cuda_sharded_linear** out);
+int32_t kanso_cuda_sharded_linear_destroy(kanso_cuda_sharded_linear* layer);
+/* The rows (row shard) or columns (K shard) this rank holds. */
+int32_t kanso_cuda_sharded_linear_range(const kanso_cuda_sharded_linear* layer, int64_t* begin,
+                                        int64_t* count);
+/* Model::linear on the sharded layer, asynchronous on the context's stream; *y_out is a device
+ * buffer owned by the layer, valid until its next forward.
+ *   row shard: x f32 [M, cols_total] (replicated). Default: y f32 [M, rows_total] gathered on
+ *     every rank (each rank's matmul stores its rows into every rank's memory, a consumer
+ *     kernel waits for the peers' signals). KANSO_SHARD_LOCAL_ONLY: y f32 [M, count], this
+ *     rank's rows only and no exchange at all: exactly the K slice a K-sharded layer wants.
+ *   K shard: x f32 [M, count] = this rank's columns of the activations; y f32 [M, rows_total],
+ *     the partial results of all ranks added in rank order (same bits on every rank).
+ * Every rank makes the same sequence of calls. A peer that never arrives ends the wait after
+ * 2 s with KANSO_ERR_TIMEOUT at the next kanso_cuda_sync. No host state changes per call, so a
+ * sequence of forwards may be captured in a CUDA graph and replayed. */
+int32_t kanso_cuda_sharded_linear_forward(kanso_cuda_sharded_linear* layer, const float* x,
+                                          int64_t M, int32_t act_mode, int32_t flags,
+                                          const float** y_out);
 /* LinearWeight::embed — src/weights.rs:50-57: dequantise the selected rows.
  * ids u32[T] (device), out f32[T, cols] (device). An id >= rows -> KANSO_ERR_SHAPE
  * is reported by the device status word at the next kanso_cuda_sync. */

@@ -17,6 +17,7 @@ DTYPE_Q8_0, DTYPE_Q4_K = 8, 12
 ACT_F32, ACT_Q8 = 0, 1
 KV_F32, KV_INT8, KV_FP8 = 0, 1, 2
 OPT_OVERLAP_WEIGHT_PREFETCH = 1
+SHARD_ROWS, SHARD_K, SHARD_LOCAL_ONLY, SHARD_HANDLE_BYTES = 0, 1, 1, 64
 Q8_BYTES, Q4K_BYTES = 34, 144
 (W_ATTN_Q, W_ATTN_K, W_ATTN_V, W_ATTN_OUTPUT, W_FFN_GATE, W_FFN_UP, W_FFN_DOWN, W_TOKEN_EMBD,
  W_OUTPUT) = range(9)
@@ -82,6 +83,14 @@ PROTOTYPES = {
     "kanso_cuda_linear_scatter_out": (_I32, [_P, _P, _P, _I64, _P, _I32, _I64, _I64, _I32]),
     "kanso_cuda_sum_shards": (_I32, [_P, _P, _I64, _I64, _I32, _P]),
     "kanso_cuda_peer_exchange": (_I32, [_P, _P, _P, _I32, _I32]),
+    "kanso_cuda_shard_group_create": (_I32, [_P, _I32, _I32, _SZ, C.POINTER(_P), _P]),
+    "kanso_cuda_shard_group_connect": (_I32, [_P, _P]),
+    "kanso_cuda_shard_group_destroy": (_I32, [_P]),
+    "kanso_cuda_sharded_linear_create": (_I32, [_P, _P, _SZ, _I32, _I64, _I64, _I32, _I64,
+                                                C.POINTER(_P)]),
+    "kanso_cuda_sharded_linear_destroy": (_I32, [_P]),
+    "kanso_cuda_sharded_linear_range": (_I32, [_P, C.POINTER(_I64), C.POINTER(_I64)]),
+    "kanso_cuda_sharded_linear_forward": (_I32, [_P, _P, _I64, _I32, _I32, C.POINTER(_P)]),
     "kanso_cuda_kv_create": (_I32, [_P, _U32, _U32, _U32, _U32, _U32, _I32, C.POINTER(_P)]),
     "kanso_cuda_kv_destroy": (_I32, [_P]),
     "kanso_cuda_kv_write_slots": (_I32, [_P, _P, _U32, _P, _P, _P, _I64, _P]),

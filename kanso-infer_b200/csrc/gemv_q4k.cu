@@ -30,9 +30,8 @@
 //     one float scale per super-block. The -dmin*m term uses exact f32 sums of x per
 //     sub-block;
 //   * per-row results of a CTA are accumulated in shared memory and written once.
-#include <cstdlib>
-
 #include "ctx.h"
+#include "shard.cuh"
 
 namespace kanso {
 
@@ -56,6 +55,10 @@ struct Q4kArgs {
   int max_rows_cta;
   // row groups per CTA: the first groups_rem CTAs take groups_quot + 1, the others groups_quot
   int groups_quot, groups_rem;
+  // sharded layer (shard != 0): the rows go to the exchange buffer of the current step in every
+  // rank's region, and the grid's last CTA signals the peers
+  int shard;
+  ShardSignal sig;
 };
 
 struct Q4kLayout {
@@ -382,17 +385,27 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   }
   cp_async_wait<0>();
   __syncthreads();
+  // exchange buffer of this step (the counter is advanced by the last CTA, after every CTA has
+  // read it here)
+  const int64_t shard_off = a.shard ? (int64_t)(*a.sig.step & 1ull) * a.sig.buf_stride : 0;
   for (int i = threadIdx.x; i < M * nrows; i += blockDim.x) {
     const int m = i / nrows, r = i - m * nrows;
     const float* p = ypart + (size_t)m * bpr * max_rows + r;
     float acc = 0.f;
     for (int S = 0; S < bpr; ++S) acc += p[S * max_rows];
-    if (a.n_out == 0) {
+    if (a.shard) {
+      for (int o = 0; o < a.sig.world; ++o)  // plain stores into every rank's region over NVLink
+        a.sig.out[o][shard_off + (int64_t)m * a.ldy + a.y_row_offset + rb + r] = acc;
+    } else if (a.n_out == 0) {
       a.y[(int64_t)m * a.ldy + rb + r] = acc;
     } else {
       for (int o = 0; o < a.n_out; ++o)  // plain stores, also into peers' memory over NVLink
         a.y_out[o][(int64_t)m * a.ldy + a.y_row_offset + rb + r] = acc;
     }
+  }
+  if (a.shard) {
+    __shared__ unsigned int s_last;
+    shard_ticket(a.sig, gridDim.x, &s_last);
   }
 }
 
@@ -432,22 +445,7 @@ static int32_t dispatch_q4k_msets(kanso_cuda_ctx* ctx, const Q4kArgs& a, int gri
   }
 }
 
-// Launch shape: warps per CTA, ring depth (0: chosen per launch), CTAs per SM.
-// KANSO_Q4K_CFG="warps,depth,ctas" overrides the default for tuning runs.
-struct Q4kCfg {
-  int nw, depth, cps;
-};
-static Q4kCfg q4k_cfg() {
-  static Q4kCfg cfg = [] {
-    Q4kCfg c{16, 0, 1};
-    if (const char* e = getenv("KANSO_Q4K_CFG")) {
-      int nw, d, cps;
-      if (sscanf(e, "%d,%d,%d", &nw, &d, &cps) == 3) c = Q4kCfg{nw, d, cps};
-    }
-    return c;
-  }();
-  return cfg;
-}
+constexpr int Q4M_NW = 16;  // warps per CTA
 
 // Sets *handled when this kernel took the call; leaves it false when the shape is outside
 // its range (the caller then uses the general streaming kernel).
@@ -460,28 +458,48 @@ int32_t q4k_direct_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, fl
   return q4k_direct_matmul_out(ctx, w, x, y, M, N, K, handled, nullptr, 0, N, 0);
 }
 
+static int32_t q4k_direct_matmul_impl(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                                      int64_t M, int64_t N, int64_t K, bool* handled,
+                                      float* const* y_out, int n_out, int64_t ld_out,
+                                      int64_t row_offset, const ShardSignal* sig);
+
 int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
                               int64_t M, int64_t N, int64_t K, bool* handled, float* const* y_out,
                               int n_out, int64_t ld_out, int64_t row_offset) {
+  return q4k_direct_matmul_impl(ctx, w, x, y, M, N, K, handled, y_out, n_out, ld_out, row_offset,
+                                nullptr);
+}
+
+// The sharded form: rows go to columns [col0, col0 + N) of the layer's exchange buffers (row
+// length ld_out) in every rank's region; the last CTA signals when sig.signal is set.
+int32_t q4k_direct_matmul_shard(kanso_cuda_ctx* ctx, const void* w, const float* x, int64_t M,
+                                int64_t N, int64_t K, bool* handled, const ShardSignal& sig,
+                                int64_t ld_out, int64_t col0) {
+  return q4k_direct_matmul_impl(ctx, w, x, nullptr, M, N, K, handled, nullptr, 0, ld_out, col0,
+                                &sig);
+}
+
+static int32_t q4k_direct_matmul_impl(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
+                                      int64_t M, int64_t N, int64_t K, bool* handled,
+                                      float* const* y_out, int n_out, int64_t ld_out,
+                                      int64_t row_offset, const ShardSignal* sig) {
   *handled = false;
   if (n_out < 0 || n_out > Q4M_MAX_OUT) return KANSO_OK;
   if (K % 256 != 0 || M < 1 || M > 8 || N < 8 || N % 8 != 0) return KANSO_OK;
-  Q4kCfg cfg = q4k_cfg();
-  int grid = ctx->sm_count * cfg.cps;
+  int grid = ctx->sm_count;
   if (N / 8 < grid) grid = (int)(N / 8);  // every CTA gets at least one group of 8 rows
   const int max_rows_cta = (int)(((N / 8 + grid - 1) / grid) * 8);
-  if (cfg.depth == 0) {
-    // The deepest ring (5..3 slots per warp) with which two CTAs fit on an SM: under
-    // dependent-launch overlap the next GEMV's CTA then moves in beside this one and has its
-    // ring filled when this kernel ends, which is worth more than the fifth slot. Shapes whose
-    // activation planes leave no room for two CTAs take four slots, or three if four do not
-    // fit at all.
-    auto total = [&](int d) { return q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, d).total; };
-    for (int d = 5; d >= 3 && !cfg.depth; --d)
-      if (2 * (total(d) + 1024) <= ctx->smem_per_sm) cfg.depth = d;  // 1 KB per CTA is reserved
-    if (!cfg.depth) cfg.depth = total(4) <= ctx->smem_optin ? 4 : 3;
-  }
-  Q4kLayout L = q4k_layout((int)K, (int)M, max_rows_cta, cfg.nw, cfg.depth);
+  // The deepest ring (5..3 slots per warp) with which two CTAs fit on an SM: under
+  // dependent-launch overlap the next GEMV's CTA then moves in beside this one and has its
+  // ring filled when this kernel ends, which is worth more than the fifth slot. Shapes whose
+  // activation planes leave no room for two CTAs take four slots, or three if four do not
+  // fit at all.
+  int depth = 0;
+  auto total = [&](int d) { return q4k_layout((int)K, (int)M, max_rows_cta, Q4M_NW, d).total; };
+  for (int d = 5; d >= 3 && !depth; --d)
+    if (2 * (total(d) + 1024) <= ctx->smem_per_sm) depth = d;  // 1 KB per CTA is reserved
+  if (!depth) depth = total(4) <= ctx->smem_optin ? 4 : 3;
+  Q4kLayout L = q4k_layout((int)K, (int)M, max_rows_cta, Q4M_NW, depth);
   if (L.total > ctx->smem_optin) return KANSO_OK;
   Q4kArgs a;
   a.w = (const uint8_t*)w;
@@ -489,7 +507,9 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
   a.y = y;
   a.rows = N;
   a.ldx = K;
-  a.ldy = n_out ? ld_out : N;
+  a.ldy = (n_out || sig) ? ld_out : N;
+  a.shard = sig ? 1 : 0;
+  a.sig = sig ? *sig : ShardSignal{};
   a.n_out = n_out;
   a.y_row_offset = row_offset;
   for (int o = 0; o < Q4M_MAX_OUT; ++o) a.y_out[o] = o < n_out ? y_out[o] : nullptr;
@@ -500,22 +520,10 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
   a.groups_quot = (int)((N / 8) / grid);
   a.groups_rem = (int)((N / 8) % grid);
   *handled = true;
-  const int key = cfg.nw * 100 + cfg.depth;
-  switch (key) {
-    case 1606: return dispatch_q4k_msets<16, 6>(ctx, a, grid, L.total);
-    case 1604: return dispatch_q4k_msets<16, 4>(ctx, a, grid, L.total);
-    case 1603: return dispatch_q4k_msets<16, 3>(ctx, a, grid, L.total);
-    case 1605: return dispatch_q4k_msets<16, 5>(ctx, a, grid, L.total);
-    case 1206: return dispatch_q4k_msets<12, 6>(ctx, a, grid, L.total);
-    case 1204: return dispatch_q4k_msets<12, 4>(ctx, a, grid, L.total);
-    case 1208: return dispatch_q4k_msets<12, 8>(ctx, a, grid, L.total);
-    case 806: return dispatch_q4k_msets<8, 6>(ctx, a, grid, L.total);
-    case 804: return dispatch_q4k_msets<8, 4>(ctx, a, grid, L.total);
-    case 808: return dispatch_q4k_msets<8, 8>(ctx, a, grid, L.total);
-    default:
-      *handled = false;
-      return fail(ctx, KANSO_ERR_CONFIG, "KANSO_Q4K_CFG: unsupported warps,depth %d,%d", cfg.nw,
-                  cfg.depth);
+  switch (depth) {
+    case 5: return dispatch_q4k_msets<Q4M_NW, 5>(ctx, a, grid, L.total);
+    case 4: return dispatch_q4k_msets<Q4M_NW, 4>(ctx, a, grid, L.total);
+    default: return dispatch_q4k_msets<Q4M_NW, 3>(ctx, a, grid, L.total);
   }
 }
 

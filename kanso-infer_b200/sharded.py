@@ -1,16 +1,15 @@
-"""One linear layer sharded over the GPUs of a node: one process per GPU, NCCL for plumbing.
+"""Test and measurement binding of the sharded layers: one process per GPU.
 
-Row sharding (W_up): rank r holds a contiguous range of output rows; y is assembled either by
-an NCCL all-gather ("nccl") or by the matmul kernel itself storing its slice into every
-peer's result buffer over NVLink ("fused", symmetric memory + one cross-GPU barrier).
-K sharding (W_down): rank r holds the blocks of a contiguous range of columns, re-packed;
-partial results are summed with an NCCL all-reduce ("nccl") or exchanged by the matmul
-kernel's own peer stores and added locally in rank order ("fused").
+Everything that matters lives behind the C ABI (kanso_cuda_shard_group_*,
+kanso_cuda_sharded_linear_*: peer-visible memory, the two-buffer exchange protocol, the
+forward call). This module only (1) carries the 64-byte memory handles between the ranks
+with torch.distributed, which is the one thing the library leaves to its caller, (2) slices
+block bytes with the library's host helpers, and (3) keeps an NCCL form of the same layers
+(mode="nccl": local matmul + all_gather / all_reduce) as the baseline to compare with.
 
-The fused modes alternate between two symmetric buffers: a rank that is one call ahead of a
-peer then never stores into the buffer that peer is still reading.
-
-This module holds no arithmetic: slicing of block bytes and calls into the C ABI.
+Row sharding (W_up): rank r holds a contiguous range of output rows. K sharding (W_down): rank r
+holds the blocks of a contiguous range of columns, re-packed; partial results are summed.
+No arithmetic here.
 """
 from __future__ import annotations
 
@@ -55,45 +54,82 @@ def k_shard(blocks: np.ndarray, dtype: int, rows: int, cols: int, rank: int, wor
     return out, begin, count
 
 
-class PeerExchange:
-    """The flag arrays and step counter of kanso_cuda_peer_exchange for one process group:
-    the cross-GPU barrier of the fused sharded layers as a kernel on the context's stream."""
+class ShardGroup:
+    """kanso_cuda_shard_group for a torch.distributed process group."""
 
     _by_group = {}
 
     @classmethod
-    def get(cls, ctx, group):
+    def get(cls, ctx, group, region_bytes=256 << 20):
         key = (id(ctx), group.group_name)
         if key not in cls._by_group:
-            cls._by_group[key] = cls(ctx, group)
+            cls._by_group[key] = cls(ctx, group, region_bytes)
         return cls._by_group[key]
 
-    def __init__(self, ctx, group):
+    def __init__(self, ctx, group, region_bytes=256 << 20):
         import torch
         import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
-        self.ctx = ctx
+        self.ctx, self.group = ctx, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        if self.world > 8:
-            raise kb.KansoError(kb.ERR_UNSUPPORTED, "peer exchange: at most 8 ranks")
-        self.flags = symm.empty((self.world,), dtype=torch.int64, device="cuda")
-        self.flags.zero_()
-        self._hdl = symm.rendezvous(self.flags, group.group_name)
-        self._ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._hdl.buffer_ptrs])
-        self.step = torch.zeros(1, dtype=torch.int64, device="cuda")
-        torch.cuda.synchronize()
-        dist.barrier(group=group)  # every rank's flags are zero before anyone signals
+        h = C.c_void_p()
+        mine = (C.c_ubyte * kb.SHARD_HANDLE_BYTES)()
+        ctx.call("kanso_cuda_shard_group_create", self.rank, self.world, region_bytes,
+                 C.byref(h), C.cast(mine, C.c_void_p))
+        self.h = h
+        # the caller's part: every rank learns every rank's handle
+        t = torch.tensor(list(mine), dtype=torch.uint8)
+        if dist.get_backend(group) == "nccl":
+            t = t.cuda()
+        gathered = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(gathered, t, group=group)
+        blob = bytes(torch.cat([g.cpu() for g in gathered]).tolist())
+        self._blob = C.create_string_buffer(blob, len(blob))
+        ctx.check(ctx.lib.kanso_cuda_shard_group_connect(self.h, C.cast(self._blob, C.c_void_p)))
+        dist.barrier(group=group)  # every rank has mapped its peers before anyone stores
 
-    def __call__(self):
-        self.ctx.call("kanso_cuda_peer_exchange", C.cast(self._ptrs, C.c_void_p),
-                      kb._ptr(self.step), self.world, self.rank)
+    def destroy(self):
+        if getattr(self, "h", None):
+            self.ctx.lib.kanso_cuda_shard_group_destroy(self.h)
+            self.h = None
 
 
-class RowShardedLinear:
-    """W[rows x cols] split by output rows; forward returns the full y on every rank."""
+class _ShardedBase:
+    def _create(self, ctx, shard, dtype, rows, cols, mode_c, max_m, group, region_bytes):
+        self.sg = ShardGroup.get(ctx, group, region_bytes)
+        h = C.c_void_p()
+        shard = np.ascontiguousarray(shard, np.uint8)
+        ctx.check(ctx.lib.kanso_cuda_sharded_linear_create(
+            self.sg.h, shard.ctypes.data, shard.nbytes, dtype, rows, cols, mode_c, max_m,
+            C.byref(h)))
+        self.h = h
+
+    def _forward(self, x, M, act_mode, flags, width):
+        import torch
+        out = C.c_void_p()
+        self.ctx.check(self.ctx.lib.kanso_cuda_sharded_linear_forward(
+            self.h, kb._ptr(x), M, act_mode, flags, C.byref(out)))
+        return _device_view(torch, out.value, M, width)
+
+    def destroy(self):
+        if getattr(self, "h", None):
+            self.ctx.lib.kanso_cuda_sharded_linear_destroy(self.h)
+            self.h = None
+
+
+def _device_view(torch, ptr, rows, cols):
+    """A torch view of rows x cols f32 at a device address the library owns."""
+    class _Arr:
+        __cuda_array_interface__ = {"shape": (rows, cols), "typestr": "<f4", "data": (ptr, False),
+                                    "version": 3}
+    return torch.as_tensor(_Arr(), device="cuda")
+
+
+class RowShardedLinear(_ShardedBase):
+    """W[rows x cols] split by output rows; forward returns the full y on every rank, or with
+    local_only=True this rank's rows only (no exchange)."""
 
     def __init__(self, ctx: kb.Context, blocks, dtype, rows, cols, group=None, mode="fused",
-                 max_m=8, presharded=False):
+                 max_m=8, presharded=False, region_bytes=256 << 20):
         """blocks: the whole [rows x cols] block matrix, or with presharded=True only this
         rank's rows (rows is always the total)."""
         import torch
@@ -107,44 +143,32 @@ class RowShardedLinear:
         else:
             shard, self.row_begin, self.row_count = row_shard(blocks, dtype, rows, cols,
                                                               self.rank, self.world)
-        self.weight = kb.Weight(ctx, shard, dtype, self.row_count, cols)
         self.max_m = max_m
         counts = [shard_range(rows, r, self.world, 8)[1] for r in range(self.world)]
         self.even = len(set(counts)) == 1
         if mode == "fused":
-            import torch.distributed._symmetric_memory as symm
-            self._bufs, self._hdls, self._ptrs, self._turn = [], [], [], 0
-            for _ in range(2):
-                buf = symm.empty((max_m, rows), dtype=torch.float32, device="cuda")
-                hdl = symm.rendezvous(buf, self.group.group_name)
-                self._bufs.append(buf)
-                self._hdls.append(hdl)
-                self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
-            self.y_full = self._bufs[0]
-            self._exchange = PeerExchange.get(ctx, self.group)
+            self._create(ctx, shard, dtype, rows, cols, kb.SHARD_ROWS, max_m, self.group,
+                         region_bytes)
         elif mode == "nccl":
+            self.weight = kb.Weight(ctx, shard, dtype, self.row_count, cols)
             self.y_full = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
             self.y_local = torch.empty((max_m, self.row_count), dtype=torch.float32, device="cuda")
         else:
             raise ValueError(mode)
 
-    def forward(self, x, M=1, act_mode=kb.ACT_F32):
-        """x: device f32 [M, cols]. Returns a view f32 [M, rows] valid on this rank."""
+    def forward(self, x, M=1, act_mode=kb.ACT_F32, local_only=False):
+        """x: device f32 [M, cols]. Returns a view f32 [M, rows] (or [M, row_count])."""
         import torch.distributed as dist
         if M > self.max_m:
             raise kb.KansoError(kb.ERR_SHAPE, f"M {M} exceeds the buffers sized for {self.max_m}")
         if self.mode == "fused":
-            # every rank stores its slice into every rank's y_full, then one exchange
-            t = self._turn
-            self._turn ^= 1
-            self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x), M,
-                          C.cast(self._ptrs[t], C.c_void_p), self.world, self.rows,
-                          self.row_begin, act_mode)
-            self._exchange()
-            self.y_full = self._bufs[t]
-            return self.y_full[:M]
+            if local_only:
+                return self._forward(x, M, act_mode, kb.SHARD_LOCAL_ONLY, self.row_count)
+            return self._forward(x, M, act_mode, 0, self.rows)
         y_local = self.y_local[:M]
         self.weight.forward(x, y_local, M, act_mode)
+        if local_only:
+            return y_local
         if M == 1 and self.even:
             dist.all_gather_into_tensor(self.y_full[0], y_local[0], group=self.group)
         else:
@@ -158,12 +182,12 @@ class RowShardedLinear:
         return self.y_full[:M]
 
 
-class KShardedLinear:
+class KShardedLinear(_ShardedBase):
     """W[rows x cols] split along K; forward takes this rank's slice of x and returns the
-    summed y on every rank (all-reduce)."""
+    summed y on every rank."""
 
     def __init__(self, ctx: kb.Context, blocks, dtype, rows, cols, group=None, max_m=8,
-                 presharded=False, mode="nccl"):
+                 presharded=False, mode="nccl", region_bytes=256 << 20):
         """blocks: the whole block matrix, or with presharded=True this rank's re-packed
         [rows x cols/world] columns (cols is always the total)."""
         import torch
@@ -178,40 +202,22 @@ class KShardedLinear:
         else:
             shard, self.col_begin, self.col_count = k_shard(blocks, dtype, rows, cols, self.rank,
                                                             self.world)
-        self.weight = kb.Weight(ctx, shard, dtype, rows, self.col_count)
-        self.y = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
         self.max_m = max_m
         if mode == "fused":
-            if self.world > 8:
-                raise kb.KansoError(kb.ERR_UNSUPPORTED, "fused K sharding: at most 8 ranks")
-            import torch.distributed._symmetric_memory as symm
-            self._bufs, self._hdls, self._ptrs, self._turn = [], [], [], 0
-            for _ in range(2):
-                buf = symm.empty((max_m, self.world * rows), dtype=torch.float32, device="cuda")
-                hdl = symm.rendezvous(buf, self.group.group_name)
-                self._bufs.append(buf)
-                self._hdls.append(hdl)
-                self._ptrs.append((C.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
-            self._exchange = PeerExchange.get(ctx, self.group)
-        elif mode != "nccl":
+            self._create(ctx, shard, dtype, rows, cols, kb.SHARD_K, max_m, self.group,
+                         region_bytes)
+        elif mode == "nccl":
+            self.weight = kb.Weight(ctx, shard, dtype, rows, self.col_count)
+            self.y = torch.empty((max_m, rows), dtype=torch.float32, device="cuda")
+        else:
             raise ValueError(mode)
 
     def forward(self, x_slice, M=1, act_mode=kb.ACT_F32):
         """x_slice: device f32 [M, col_count] = columns [col_begin, col_begin + col_count) of x."""
         import torch.distributed as dist
-        y = self.y[:M]
         if self.mode == "fused":
-            # every rank stores its partial y into its slice of every rank's buffer; after
-            # one exchange each rank adds the slices itself, in rank order
-            t = self._turn
-            self._turn ^= 1
-            self.ctx.call("kanso_cuda_linear_scatter_out", self.weight.h, kb._ptr(x_slice), M,
-                          C.cast(self._ptrs[t], C.c_void_p), self.world, self.world * self.rows,
-                          self.rank * self.rows, act_mode)
-            self._exchange()
-            self.ctx.call("kanso_cuda_sum_shards", kb._ptr(self._bufs[t]), M, self.rows,
-                          self.world, kb._ptr(y))
-            return y
+            return self._forward(x_slice, M, act_mode, 0, self.rows)
+        y = self.y[:M]
         self.weight.forward(x_slice, y, M, act_mode)
         dist.all_reduce(y, group=self.group)
         return y

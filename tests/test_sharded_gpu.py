@@ -1,5 +1,9 @@
-"""GPU, 2 ranks over NCCL: row-sharded (all-gather, NCCL and fused peer-store) and K-sharded
-(all-reduce) GEMV against the unsharded oracle. Skipped when fewer than 2 GPUs are visible."""
+"""GPU: the sharded layers behind the C ABI against the unsharded oracle.
+
+One test runs the whole protocol on a single GPU as a group of one rank (signal, wait, copy-out
+and sum go through the same kernels); the other runs 2 ranks over NCCL (row-sharded with the
+gather, row-sharded feeding a K-sharded layer, batches on the tensor-core path, a captured
+graph replayed) and is skipped when fewer than 2 GPUs are visible."""
 import os
 import socket
 
@@ -66,6 +70,54 @@ def _worker(rank, world, port, q):
                     torch.cuda.synchronize()
                     assert rel(y.cpu().numpy(), ref) <= 1e-3, ("k", mode, M)
                     dist.barrier()
+        # the FFN pair as it is meant to run: the row-sharded up projection keeps its slice on
+        # the rank (no exchange), which is exactly the K slice of the K-sharded down projection
+        w2 = (rng.standard_normal((512, rows)) * 0.02).astype(np.float32)
+        b2 = O.quantize_weights_q4_k(w2)
+        up = sh.RowShardedLinear(ctx, blocks, kb.DTYPE_Q4_K, rows, cols, mode="fused", max_m=64)
+        down = sh.KShardedLinear(ctx, b2, kb.DTYPE_Q4_K, 512, rows, mode="fused", max_m=64)
+        for M in (1, 64):  # 64 rows take the tensor-core GEMM and the scatter kernel
+            x = rng.standard_normal((M, cols)).astype(np.float32)
+            h_ref = O.gemm_q4_k(blocks, x, M, rows, cols)
+            y_ref = O.gemm_q4_k(b2, h_ref, M, 512, rows)
+            xd = torch.from_numpy(x).cuda()
+            for _ in range(3):
+                h = up.forward(xd, M, local_only=True)
+                y = down.forward(h, M)
+                ctx.sync()
+                torch.cuda.synchronize()
+                assert rel(y.cpu().numpy(), y_ref) <= 2e-3, ("pair", M)
+                full = up.forward(xd, M)
+                ctx.sync()
+                torch.cuda.synchronize()
+                assert rel(full.cpu().numpy(), h_ref) <= 1e-3, ("gather", M)
+            dist.barrier()
+        # a captured graph of three pairs replayed: the buffer choice follows the device's step
+        # counter, so the replays alternate buffers correctly although the host is not involved
+        x = rng.standard_normal((1, cols)).astype(np.float32)
+        xd = torch.from_numpy(x).cuda()
+        y_ref = O.gemm_q4_k(b2, O.gemm_q4_k(blocks, x, 1, rows, cols), 1, 512, rows)
+        ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 1)
+        keep = torch.empty((3, 512), device="cuda")
+
+        def three():
+            for i in range(3):
+                keep[i].copy_(down.forward(up.forward(xd, 1, local_only=True), 1)[0])
+        three()
+        ctx.sync()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            three()
+        for _ in range(5):
+            g.replay()
+        ctx.sync()
+        torch.cuda.synchronize()
+        for i in range(3):
+            assert rel(keep[i].cpu().numpy(), y_ref[0]) <= 2e-3, ("graph", i)
+        dist.barrier()
+        ctx.set_option(kb.OPT_OVERLAP_WEIGHT_PREFETCH, 0)
         # Q8_0 takes the general path (slice to scratch, then a scatter kernel)
         b8 = O.quantize_weights_q8_0(w[:512])
         x = rng.standard_normal((1, cols)).astype(np.float32)
@@ -97,3 +149,58 @@ def test_sharded_linear_two_gpus(torch_cuda):
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_sharded_layers_as_a_group_of_one(ctx, kb, oracle, torch_cuda):
+    """The C-ABI objects with world = 1: create / connect / layers / forward. The producing
+    kernel signals this rank's own flag, the consumer waits for it and copies or sums, so every
+    kernel of the multi-GPU path runs; repeated calls alternate the two exchange buffers."""
+    import ctypes as C
+    torch = torch_cuda
+    sh = package().sharded
+    rng = np.random.Generator(np.random.PCG64(0xB2000C10))
+    rows, cols = 512, 2048
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    blocks = oracle.quantize_weights_q4_k(w)
+    h, handle = C.c_void_p(), (C.c_ubyte * kb.SHARD_HANDLE_BYTES)()
+    ctx.call("kanso_cuda_shard_group_create", 0, 1, 32 << 20, C.byref(h), C.cast(handle, C.c_void_p))
+    ctx.check(ctx.lib.kanso_cuda_shard_group_connect(h, C.cast(handle, C.c_void_p)))
+    layers = {}
+    for name, mode in (("rows", kb.SHARD_ROWS), ("k", kb.SHARD_K)):
+        lh = C.c_void_p()
+        ctx.check(ctx.lib.kanso_cuda_sharded_linear_create(h, blocks.ctypes.data, blocks.nbytes,
+                                                           kb.DTYPE_Q4_K, rows, cols, mode, 40,
+                                                           C.byref(lh)))
+        b, c = C.c_int64(), C.c_int64()
+        assert ctx.lib.kanso_cuda_sharded_linear_range(lh, C.byref(b), C.byref(c)) == 0
+        assert (b.value, c.value) == ((0, rows) if name == "rows" else (0, cols))
+        layers[name] = lh
+    for M in (1, 5, 8, 40):
+        x = rng.standard_normal((M, cols)).astype(np.float32)
+        ref = oracle.gemm_q4_k(blocks, x, M, rows, cols)
+        xd = torch.from_numpy(x).cuda()
+        for name, lh in layers.items():
+            for flags in ((0, kb.SHARD_LOCAL_ONLY) if name == "rows" else (0,)):
+                for _ in range(3):
+                    out = C.c_void_p()
+                    ctx.check(ctx.lib.kanso_cuda_sharded_linear_forward(lh, xd.data_ptr(), M,
+                                                                        kb.ACT_F32, flags,
+                                                                        C.byref(out)))
+                    ctx.sync()
+                    got = sh._device_view(torch, out.value, M, rows).cpu().numpy()
+                    err = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+                    assert err <= 1e-3, (name, M, flags, err)
+    # misuse: too many rows, unknown mode, a region that is too small
+    out = C.c_void_p()
+    assert ctx.lib.kanso_cuda_sharded_linear_forward(layers["k"], xd.data_ptr(), 41, kb.ACT_F32, 0,
+                                                     C.byref(out)) == kb.ERR_SHAPE
+    lh = C.c_void_p()
+    assert ctx.lib.kanso_cuda_sharded_linear_create(h, blocks.ctypes.data, blocks.nbytes,
+                                                    kb.DTYPE_Q4_K, rows, cols, 7, 8,
+                                                    C.byref(lh)) == kb.ERR_CONFIG
+    assert ctx.lib.kanso_cuda_sharded_linear_create(h, blocks.ctypes.data, blocks.nbytes,
+                                                    kb.DTYPE_Q4_K, rows, cols, kb.SHARD_K, 100000,
+                                                    C.byref(lh)) == kb.ERR_CONFIG
+    for lh in layers.values():
+        ctx.lib.kanso_cuda_sharded_linear_destroy(lh)
+    ctx.lib.kanso_cuda_shard_group_destroy(h)
