@@ -122,6 +122,10 @@ int32_t kanso_cuda_ctx_set_option(kanso_cuda_ctx* ctx, int32_t option, int32_t v
 uint64_t kanso_cuda_launch_count(const kanso_cuda_ctx* ctx);
 /* Number of streaming multiprocessors of the context's device. */
 int32_t kanso_cuda_sm_count(const kanso_cuda_ctx* ctx);
+/* Measurement aid, no counterpart in the reference: one launch that only reads `nbytes` of a
+ * device buffer with 128-bit loads. Timed beside a GEMV over the same buffer it gives the floor
+ * that launch latency and the memory system put under that GEMV. */
+int32_t kanso_cuda_probe_read(kanso_cuda_ctx* ctx, const void* buf, size_t nbytes);
 
 /* ------------------------------------------------------------------------- */
 /* Block kernels: src/quant. All pointers are device pointers, 16-byte aligned. */

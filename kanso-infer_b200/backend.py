@@ -63,6 +63,7 @@ PROTOTYPES = {
     "kanso_cuda_ctx_set_option": (_I32, [_P, _I32, _I32]),
     "kanso_cuda_launch_count": (_U64, [_P]),
     "kanso_cuda_sm_count": (_I32, [_P]),
+    "kanso_cuda_probe_read": (_I32, [_P, _P, _SZ]),
     "kanso_cuda_gemv_q8_0": (_I32, [_P, _P, _P, _P, _I64, _I64]),
     "kanso_cuda_gemv_q4_k": (_I32, [_P, _P, _P, _P, _I64, _I64]),
     "kanso_cuda_gemm_q8_0": (_I32, [_P, _P, _P, _P, _I64, _I64, _I64, _I32]),

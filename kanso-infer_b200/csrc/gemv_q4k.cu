@@ -385,27 +385,35 @@ __global__ void __launch_bounds__(Q4M_WARPS * 32, 1024 / (Q4M_WARPS * 32)) gemv_
   }
   cp_async_wait<0>();
   __syncthreads();
-  // exchange buffer of this step (the counter is advanced by the last CTA, after every CTA has
-  // read it here)
-  const int64_t shard_off = a.shard ? (int64_t)(*a.sig.step & 1ull) * a.sig.buf_stride : 0;
   for (int i = threadIdx.x; i < M * nrows; i += blockDim.x) {
     const int m = i / nrows, r = i - m * nrows;
     const float* p = ypart + (size_t)m * bpr * max_rows + r;
     float acc = 0.f;
     for (int S = 0; S < bpr; ++S) acc += p[S * max_rows];
-    if (a.shard) {
-      for (int o = 0; o < a.sig.world; ++o)  // plain stores into every rank's region over NVLink
-        a.sig.out[o][shard_off + (int64_t)m * a.ldy + a.y_row_offset + rb + r] = acc;
-    } else if (a.n_out == 0) {
-      a.y[(int64_t)m * a.ldy + rb + r] = acc;
+    if (a.n_out == 0) {
+      a.y[(int64_t)m * a.ldy + rb + r] = acc;  // sharded layer: y is the local staging slice
     } else {
       for (int o = 0; o < a.n_out; ++o)  // plain stores, also into peers' memory over NVLink
         a.y_out[o][(int64_t)m * a.ldy + a.y_row_offset + rb + r] = acc;
     }
   }
   if (a.shard) {
-    __shared__ unsigned int s_last;
-    shard_ticket(a.sig, gridDim.x, &s_last);
+    // Sharded layer: the CTA that draws the last ticket publishes the whole slice to the peers
+    // and, for a K shard, waits for theirs and adds them up (shard_tail); all others are done.
+    // (the flag lives in dynamic shared memory that the main loop no longer needs: a static
+    // variable would come off the opt-in maximum the launch asks for)
+    volatile unsigned int* s_last = reinterpret_cast<volatile unsigned int*>(smem + L.off_dxs);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int drawn = atomicAdd(a.sig.ticket, 1u);
+      *s_last = drawn == gridDim.x - 1;
+      if (*s_last) *a.sig.ticket = 0;  // every CTA has drawn: ready for the next launch
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    shard_tail(a.sig);
   }
 }
 
@@ -470,13 +478,13 @@ int32_t q4k_direct_matmul_out(kanso_cuda_ctx* ctx, const void* w, const float* x
                                 nullptr);
 }
 
-// The sharded form: rows go to columns [col0, col0 + N) of the layer's exchange buffers (row
-// length ld_out) in every rank's region; the last CTA signals when sig.signal is set.
-int32_t q4k_direct_matmul_shard(kanso_cuda_ctx* ctx, const void* w, const float* x, int64_t M,
-                                int64_t N, int64_t K, bool* handled, const ShardSignal& sig,
-                                int64_t ld_out, int64_t col0) {
-  return q4k_direct_matmul_impl(ctx, w, x, nullptr, M, N, K, handled, nullptr, 0, ld_out, col0,
-                                &sig);
+// The sharded form: this pass's rows go to `stage` (this rank's memory); the grid's last CTA runs
+// shard_tail (publish to the peers, signal, and for a K shard wait and sum) when sig.signal is
+// set, i.e. on the last pass.
+int32_t q4k_direct_matmul_shard(kanso_cuda_ctx* ctx, const void* w, const float* x, float* stage,
+                                int64_t M, int64_t N, int64_t K, bool* handled,
+                                const ShardSignal& sig) {
+  return q4k_direct_matmul_impl(ctx, w, x, stage, M, N, K, handled, nullptr, 0, N, 0, &sig);
 }
 
 static int32_t q4k_direct_matmul_impl(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y,
@@ -507,7 +515,7 @@ static int32_t q4k_direct_matmul_impl(kanso_cuda_ctx* ctx, const void* w, const 
   a.y = y;
   a.rows = N;
   a.ldx = K;
-  a.ldy = (n_out || sig) ? ld_out : N;
+  a.ldy = n_out ? ld_out : N;
   a.shard = sig ? 1 : 0;
   a.sig = sig ? *sig : ShardSignal{};
   a.n_out = n_out;

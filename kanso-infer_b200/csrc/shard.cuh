@@ -17,6 +17,14 @@ struct ShardSignal {
   int64_t buf_stride;                         // floats between the two exchange buffers
   int world, rank;
   int signal;                                 // 0: an earlier pass of a multi-pass matmul
+  // The fused tail of the Q4_K matmul (shard_tail below): all rows of all passes, staged in
+  // this rank's memory, and what to do with them.
+  const float* stage;   // [m_total, n] this rank's slice
+  float* y;             // K shard: the summed result [m_total, n]; row shard: unused
+  int64_t ld, col0, n;  // row length of an exchange buffer, first column and width of the slice
+  int m_total;
+  int sum;              // 1: K shard (wait for the peers and add the partial results)
+  int* status;          // the context's device status word
 };
 
 // The last CTA of the producing grid calls this after every CTA's stores are fenced.
@@ -34,15 +42,79 @@ __device__ __forceinline__ void shard_publish(const ShardSignal& s) {
 // Called by every CTA of a producing grid after its stores; `s_last` is a shared-memory word.
 __device__ __forceinline__ void shard_ticket(const ShardSignal& s, unsigned int total_ctas,
                                              unsigned int* s_last) {
-  __threadfence_system();  // this thread's stores to the peers are performed system-wide
+  // One system-scope fence per CTA, not per thread (75 000 of them cost 20 us per launch): the
+  // CTA barrier orders every thread's stores before thread 0, whose fence is cumulative over
+  // what it has observed, so the stores are performed system-wide before the ticket is drawn.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int drawn = atomicAdd(s.ticket, 1u);
     *s_last = drawn == total_ctas - 1;
     if (*s_last) {
       __threadfence();
       shard_publish(s);
     }
+  }
+}
+
+// Bounded wait until every peer's slot of this rank's flag array has reached `e` (threads
+// 0..world-1 of the CTA poll, 2 s at most).
+__device__ __forceinline__ void shard_wait_flags(const unsigned long long* mine, int world,
+                                                 unsigned long long e, int* status) {
+  if ((int)threadIdx.x < world) {
+    unsigned long long t0, t1, seen;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];"
+                   : "=l"(seen)
+                   : "l"(mine + threadIdx.x)
+                   : "memory");
+      if (seen >= e) break;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {  // 2 s
+        atomicOr(status, (int)DEV_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+}
+
+// The fused tail of a sharded Q4_K matmul with few activation rows, run by the ONE CTA that
+// drew the grid's last ticket (every other CTA has stored its rows into `stage`, fenced and
+// left, so the kernel after this one may already be fetching its weights): the slice goes into
+// the current exchange buffer of every rank with plain stores, one system-scope fence, the
+// step advances and the peers are signalled; a K shard then waits for the peers' signals and
+// adds the partial results in rank order into y. Compute and collective are one kernel.
+__device__ __forceinline__ void shard_tail(const ShardSignal& s) {
+  if (!s.signal) return;  // an earlier pass: its rows are published by the last pass
+  const unsigned long long e = *s.step + 1;
+  const int64_t par = (int64_t)((e - 1) & 1ull) * s.buf_stride;
+  const int64_t total = (int64_t)s.m_total * s.n;
+  for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const int64_t m = i / s.n, c = i - m * s.n;
+    const float v = __ldcg(s.stage + i);
+    for (int r = 0; r < s.world; ++r) s.out[r][par + m * s.ld + s.col0 + c] = v;
+  }
+  // one system-scope fence per storing thread, then thread r tells rank r (one store each, in
+  // parallel: a release store per peer from one thread would pay a fence per peer)
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < s.world)
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s.flags[threadIdx.x] + s.rank),
+                 "l"(e)
+                 : "memory");
+  if (threadIdx.x == 0) *s.step = e;
+  if (!s.sum) return;
+  shard_wait_flags(s.flags[s.rank], s.world, e, s.status);
+  const float* buf = s.out[s.rank] + par;  // this rank's own copy of the exchange buffer
+  for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const int64_t m = i / s.n, c = i - m * s.n;
+    const float* p = buf + m * s.ld + c;
+    float acc = 0.f;
+    for (int r = 0; r < s.world; ++r) acc += __ldcg(p + (int64_t)r * s.n);
+    s.y[i] = acc;
   }
 }
 

@@ -51,6 +51,7 @@ struct kanso_cuda_sharded_linear {
   int64_t ld = 0;                      // floats per row of an exchange buffer
   float* y = nullptr;                  // fixed result [max_m, rows_total]
   float* y_slice = nullptr;            // row shard: this rank's rows only [max_m, count]
+  float* stage = nullptr;              // few-row Q4_K path: this rank's slice before it is published
   int slot = 0;
 };
 
@@ -79,29 +80,6 @@ __global__ void shard_scatter_signal_kernel(const float* __restrict__ src, Shard
     for (int r = 0; r < s.world; ++r) s.out[r][par * s.buf_stride + m * ld + col0 + c] = v;
   }
   shard_ticket(s, gridDim.x, &s_last);
-}
-
-// Bounded wait until every peer's slot of this rank's flag array has reached `e`.
-__device__ __forceinline__ void shard_wait_flags(const unsigned long long* mine, int world,
-                                                 unsigned long long e, int* status) {
-  if ((int)threadIdx.x < world) {
-    unsigned long long t0, t1, seen;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
-    for (;;) {
-      asm volatile("ld.acquire.sys.global.u64 %0, [%1];"
-                   : "=l"(seen)
-                   : "l"(mine + threadIdx.x)
-                   : "memory");
-      if (seen >= e) break;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-      if (t1 - t0 > 2000000000ull) {  // 2 s
-        atomicOr(status, (int)DEV_WAIT_TIMEOUT);
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
-  __syncthreads();
 }
 
 // Row shard, gathered: copies buffer ((step - 1) & 1) [M, ld] to the fixed result.
@@ -147,9 +125,9 @@ __global__ void shard_wait_sum_kernel(const float* __restrict__ buf0, int64_t bu
 using namespace kanso;
 
 namespace kanso {
-int32_t q4k_direct_matmul_shard(kanso_cuda_ctx* ctx, const void* w, const float* x, int64_t M,
-                                int64_t N, int64_t K, bool* handled, const ShardSignal& sig,
-                                int64_t ld_out, int64_t col0);
+int32_t q4k_direct_matmul_shard(kanso_cuda_ctx* ctx, const void* w, const float* x, float* stage,
+                                int64_t M, int64_t N, int64_t K, bool* handled,
+                                const ShardSignal& sig);
 
 static unsigned long long* sg_flags(const kanso_cuda_shard_group* g, int r, int slot) {
   return reinterpret_cast<unsigned long long*>(g->peer[r] + (size_t)slot * SG_CTRL_SLOT);
@@ -181,26 +159,39 @@ static ShardSignal sg_signal(const kanso_cuda_sharded_linear* L, int signal) {
 // rank, followed by the signal. Q4_K with up to 8 activation rows stores from the matmul's own
 // epilogue; every other shape goes through a staging buffer and the scatter kernel.
 static int32_t sg_produce(kanso_cuda_sharded_linear* L, const float* x, int64_t M, int64_t n,
-                          int64_t K, int64_t col0, int32_t act_mode) {
+                          int64_t K, int64_t col0, int32_t act_mode, bool* fused) {
   kanso_cuda_ctx* ctx = L->g->ctx;
+  *fused = false;
   if (L->w->dtype == KANSO_DTYPE_Q4_K && act_mode == KANSO_ACT_F32 && M <= 8) {
-    // up to 6 rows in one pass; 7 and 8 rows in two passes of 4, the last one signals
+    // Up to 6 rows in one pass; 7 and 8 rows in two passes of 4. Every pass stores its rows into
+    // the layer's staging slice; the last CTA of the LAST pass publishes all rows, signals, and
+    // for a K shard waits for the peers and sums: one kernel per forward, no separate consumer.
     const int64_t mp = M > 6 ? 4 : M;
     bool all = true;
     for (int64_t m0 = 0; m0 < M && all; m0 += mp) {
       const int64_t mc = M - m0 < mp ? M - m0 : mp;
       ShardSignal s = sg_signal(L, m0 + mc >= M ? 1 : 0);
-      for (int r = 0; r < s.world; ++r) s.out[r] += m0 * L->ld;
+      s.stage = L->stage;
+      s.y = L->y;
+      s.ld = L->ld;
+      s.col0 = col0;
+      s.n = n;
+      s.m_total = (int)M;
+      s.sum = L->mode == KANSO_SHARD_K ? 1 : 0;
+      s.status = ctx->dev_status;
       bool handled = false;
-      int32_t st = q4k_direct_matmul_shard(ctx, L->w->dev, x + m0 * K, mc, n, K, &handled, s,
-                                           L->ld, col0);
+      int32_t st = q4k_direct_matmul_shard(ctx, L->w->dev, x + m0 * K, L->stage + m0 * n, mc, n, K,
+                                           &handled, s);
       if (st) return st;
       if (!handled) {
         if (m0 != 0) return fail(ctx, KANSO_ERR_DEVICE, "sharded matmul: inconsistent passes");
         all = false;
       }
     }
-    if (all) return KANSO_OK;
+    if (all) {
+      *fused = true;
+      return KANSO_OK;
+    }
   }
   int32_t st = ctx_stage_dev(ctx, sizeof(float) * (size_t)M * (size_t)n);
   if (st) return st;
@@ -339,6 +330,9 @@ int32_t kanso_cuda_sharded_linear_create(kanso_cuda_shard_group* g, const void* 
     e = cudaMalloc(&L->y, sizeof(float) * (size_t)max_m * (size_t)rows_total);
     if (e == cudaSuccess && mode == KANSO_SHARD_ROWS)
       e = cudaMalloc(&L->y_slice, sizeof(float) * (size_t)max_m * (size_t)count);
+    if (e == cudaSuccess)
+      e = cudaMalloc(&L->stage, sizeof(float) * 8 *
+                                    (size_t)(mode == KANSO_SHARD_ROWS ? count : rows_total));
     if (e != cudaSuccess) st = cuda_fail(ctx, e, "sharded_linear_create");
   }
   if (st != KANSO_OK) {
@@ -355,6 +349,7 @@ int32_t kanso_cuda_sharded_linear_destroy(kanso_cuda_sharded_linear* L) {
   if (L->w) kanso_cuda_weight_free(L->w);
   if (L->y) cudaFree(L->y);
   if (L->y_slice) cudaFree(L->y_slice);
+  if (L->stage) cudaFree(L->stage);
   delete L;
   return KANSO_OK;
 }
@@ -388,7 +383,8 @@ int32_t kanso_cuda_sharded_linear_forward(kanso_cuda_sharded_linear* L, const fl
       *y_out = L->y_slice;
       return st;
     }
-    int32_t st = sg_produce(L, x, M, L->count, L->cols_total, L->begin, act_mode);
+    bool fused = false;
+    int32_t st = sg_produce(L, x, M, L->count, L->cols_total, L->begin, act_mode, &fused);
     if (st) return st;
     int64_t blocks = (M * L->ld + 255) / 256;
     if (blocks > 2 * ctx->sm_count) blocks = 2 * ctx->sm_count;
@@ -401,9 +397,12 @@ int32_t kanso_cuda_sharded_linear_forward(kanso_cuda_sharded_linear* L, const fl
     return after_launch(ctx, "shard wait/copy");
   }
   // K shard: x is this rank's columns [begin, begin + count) of the activations
+  bool fused = false;
   int32_t st = sg_produce(L, x, M, L->rows_total, L->count, (int64_t)g->rank * L->rows_total,
-                          act_mode);
+                          act_mode, &fused);
   if (st) return st;
+  *y_out = L->y;
+  if (fused) return KANSO_OK;  // the matmul's last CTA has waited for the peers and summed
   int64_t blocks = (M * L->rows_total + 255) / 256;
   if (blocks > 2 * ctx->sm_count) blocks = 2 * ctx->sm_count;
   KANSO_CUDA_TRY(ctx,
