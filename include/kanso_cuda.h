@@ -330,6 +330,21 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
                                    const uint32_t* context_lens, float* out,
                                    const kanso_paged_attention_params* params,
                                    const uint32_t* host_context_lens);
+/* Chunked-prefill attention, query_len > 1: the attention of Model::forward_prefill and of the
+ * mixed batches of forward_batch_rows (src/model.rs:1002-1099,1470-1529) over the int8 pool.
+ * The chunk's K/V must already be in the pool (kanso_cuda_kv_write_slots). Sequence s has
+ * host_query_lens[s] query tokens, the LAST tokens of its host_context_lens[s] (which counts the
+ * chunk); query i attends keys 0 ..= context - query_len + i, which is what the reference's
+ * offset causal mask of -1e9 leaves (src/model.rs:1027-1043). q and out f32
+ * [sum of query_lens, num_heads*head_dim], rows in sequence order; block_tables device
+ * u32[num_seqs*max_blocks]; the two length arrays are HOST arrays (they are host slices in the
+ * reference's forward_batch, src/model.rs:1360-1369). */
+int32_t kanso_cuda_paged_attention_prefill(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
+                                           uint32_t layer, const float* q,
+                                           const uint32_t* block_tables,
+                                           const uint32_t* host_context_lens,
+                                           const uint32_t* host_query_lens, float* out,
+                                           const kanso_paged_attention_params* params);
 /* The same decode attention for callers that cannot allocate device memory. It has no
  * counterpart in the reference. kanso_cuda_paged_attention keeps its split-context partials
  * in context scratch that grows with cudaMalloc when a larger batch arrives; an engine whose
@@ -375,6 +390,21 @@ int32_t kanso_cuda_residual_add(kanso_cuda_ctx* ctx, float* hidden, const float*
 int32_t kanso_cuda_model_create(kanso_cuda_ctx* ctx, const kanso_model_config* cfg,
                                 kanso_cuda_model** out);
 int32_t kanso_cuda_model_destroy(kanso_cuda_model* m);
+/* ModelWeights::load_from_gguf — src/weights.rs:332-493: reads a .gguf file (metadata keys
+ * general.architecture, llama.block_count, llama.attention.head_count[_kv],
+ * llama.embedding_length, llama.feed_forward_length, llama.attention.layer_norm_rms_epsilon
+ * (default 1e-5), llama.rope.freq_base (default 10000); tensors token_embd.weight,
+ * output_norm.weight, optional output.weight (absent = tied lm_head), blk.N.{attn_norm, attn_q,
+ * attn_k, attn_v, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down}.weight), creates the model
+ * and uploads every tensor. The Q and K projections' rows are permuted from llama.cpp's
+ * interleaved head layout to rotate-half on the way (interleaved_permutation,
+ * src/weights.rs:231-252; the reference permutes the projected activations instead,
+ * src/model.rs:455-477). block_size / max_seq_len 0 = the loader's 16 / 2048. A missing key,
+ * tensor or an unsupported architecture is KANSO_ERR_CONFIG with the reference's message;
+ * 'granite' is recognised and refused (its multipliers are not wired). cfg_out may be NULL. */
+int32_t kanso_cuda_model_load_gguf(kanso_cuda_ctx* ctx, const char* path, uint32_t block_size,
+                                   uint32_t max_seq_len, kanso_cuda_model** out,
+                                   kanso_model_config* cfg_out);
 /* Projection weights: GGUF blocks in host memory (copied to the device). */
 int32_t kanso_cuda_model_set_weight(kanso_cuda_model* m, uint32_t layer, int32_t which,
                                     const void* host_bytes, size_t nbytes, int32_t dtype,

@@ -100,6 +100,8 @@ PROTOTYPES = {
     "kanso_cuda_kv_bytes_per_token": (_U64, [_P]),
     "kanso_cuda_paged_attention": (_I32, [_P, _P, _U32, _P, _P, _P, _P,
                                           C.POINTER(PagedAttentionParams), _P]),
+    "kanso_cuda_paged_attention_prefill": (_I32, [_P, _P, _U32, _P, _P, _P, _P, _P,
+                                                  C.POINTER(PagedAttentionParams)]),
     "kanso_cuda_paged_attention_noalloc": (_I32, [_P, _P, _U32, _P, _P, _P, _P,
                                                   C.POINTER(PagedAttentionParams), _P]),
     "kanso_cuda_validate_paged_attention_params": (_I32, [C.POINTER(PagedAttentionParams),
@@ -110,6 +112,8 @@ PROTOTYPES = {
     "kanso_cuda_residual_add": (_I32, [_P, _P, _P, _I64]),
     "kanso_cuda_model_create": (_I32, [_P, C.POINTER(ModelConfig), C.POINTER(_P)]),
     "kanso_cuda_model_destroy": (_I32, [_P]),
+    "kanso_cuda_model_load_gguf": (_I32, [_P, C.c_char_p, _U32, _U32, C.POINTER(_P),
+                                          C.POINTER(ModelConfig)]),
     "kanso_cuda_model_set_weight": (_I32, [_P, _U32, _I32, _P, _SZ, _I32, _I64, _I64]),
     "kanso_cuda_model_set_norm": (_I32, [_P, _U32, _I32, _P, _I64]),
     "kanso_cuda_decode_step": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _I32, _P]),
@@ -328,6 +332,13 @@ class KvPool:
                       _ptr(context_lens), _ptr(out), C.byref(params), _ptr(host_context_lens))
 
 
+    def paged_attention_prefill(self, layer, q, block_tables, host_context_lens,
+                                host_query_lens, out, params: PagedAttentionParams):
+        """Chunked-prefill attention; the two length arrays are host uint32 arrays."""
+        self.ctx.call("kanso_cuda_paged_attention_prefill", self.h, layer, _ptr(q),
+                      _ptr(block_tables), _ptr(host_context_lens), _ptr(host_query_lens),
+                      _ptr(out), C.byref(params))
+
     def paged_attention_noalloc(self, layer, q, block_tables, context_lens, out,
                                 params: PagedAttentionParams, host_context_lens=None):
         """Same call with the partials in the library's built-in array (no allocation)."""
@@ -351,6 +362,17 @@ class Model:
         h = _P()
         ctx.call("kanso_cuda_model_create", C.byref(cfg), C.byref(h))
         self.h = h
+
+    @classmethod
+    def from_gguf(cls, ctx: Context, path: str, block_size: int = 0, max_seq_len: int = 0):
+        """ModelWeights::load_from_gguf (src/weights.rs:332-493)."""
+        self = cls.__new__(cls)
+        self.ctx, self.cfg = ctx, ModelConfig()
+        h = _P()
+        ctx.call("kanso_cuda_model_load_gguf", path.encode(), block_size, max_seq_len, C.byref(h),
+                 C.byref(self.cfg))
+        self.h = h
+        return self
 
     def destroy(self):
         if getattr(self, "h", None):

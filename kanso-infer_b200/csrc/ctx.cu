@@ -42,6 +42,7 @@ void* ctx_scratch(kanso_cuda_ctx* ctx, size_t bytes) {
     return nullptr;
   }
   ctx->scratch_bytes = want;
+  ctx->buf_gen++;
   return ctx->scratch;
 }
 
@@ -53,6 +54,7 @@ int32_t ctx_pinned(kanso_cuda_ctx* ctx, size_t bytes) {
   ctx->pinned_bytes = 0;
   KANSO_CUDA_TRY(ctx, cudaMallocHost(&ctx->pinned, bytes), "pinned staging allocation");
   ctx->pinned_bytes = bytes;
+  ctx->buf_gen++;
   return KANSO_OK;
 }
 
@@ -64,6 +66,7 @@ int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes) {
   ctx->stage_dev_bytes = 0;
   KANSO_CUDA_TRY(ctx, cudaMalloc(&ctx->stage_dev, bytes), "device staging allocation");
   ctx->stage_dev_bytes = bytes;
+  ctx->buf_gen++;
   return KANSO_OK;
 }
 
@@ -168,6 +171,13 @@ int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx) {
                                  cudaMemcpyDeviceToHost, ctx->stream),
                  "status word read");
   KANSO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream), "stream synchronize");
+  return status_word_result(ctx);
+}
+
+}  // extern "C"
+
+namespace kanso {
+int32_t status_word_result(kanso_cuda_ctx* ctx) {
   const int st = *ctx->host_status;
   if (st != 0) {
     cudaMemset(ctx->dev_status, 0, sizeof(int));
@@ -180,6 +190,9 @@ int32_t kanso_cuda_sync(kanso_cuda_ctx* ctx) {
   }
   return KANSO_OK;
 }
+}  // namespace kanso
+
+extern "C" {
 
 const char* kanso_cuda_last_error(const kanso_cuda_ctx* ctx) {
   return ctx ? ctx->last_error.c_str() : g_no_ctx_error.c_str();

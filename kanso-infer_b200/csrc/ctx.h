@@ -33,6 +33,19 @@ struct kanso_cuda_ctx {
   size_t pinned_bytes = 0;
   void* stage_dev = nullptr;
   size_t stage_dev_bytes = 0;
+  // bumped whenever scratch, pinned or device staging is reallocated: captured graphs that
+  // hold the old addresses are stale
+  uint64_t buf_gen = 0;
+};
+
+// One captured host call of a weight (kanso_cuda_linear_host): copy in, matmul, copy out and
+// status word as a single graph launch.
+struct kanso_host_graph {
+  int64_t M = 0;
+  int32_t act_mode = 0;
+  uint64_t buf_gen = 0;
+  bool overlap = false;
+  cudaGraphExec_t exec = nullptr;  // nullptr: capture was tried and is not possible
 };
 
 struct kanso_cuda_weight {
@@ -41,6 +54,8 @@ struct kanso_cuda_weight {
   size_t nbytes = 0;
   int32_t dtype = 0;
   int64_t rows = 0, cols = 0;
+  uint32_t host_calls = 0;
+  std::vector<kanso_host_graph> host_graphs;
 };
 
 namespace kanso {
@@ -54,6 +69,8 @@ int32_t ctx_pinned(kanso_cuda_ctx* ctx, size_t bytes);
 int32_t ctx_stage_dev(kanso_cuda_ctx* ctx, size_t bytes);
 // Checks the launch, counts it.
 int32_t after_launch(kanso_cuda_ctx* ctx, const char* what);
+// Turns the status word that has landed in ctx->host_status into a return code (and clears it).
+int32_t status_word_result(kanso_cuda_ctx* ctx);
 
 // Asks, once per device, for the largest shared-memory carveout for `kern`. A launch that
 // overlaps the kernel before it can only share an SM with it when both run under the same

@@ -19,6 +19,7 @@
 // every CTA publishes its partials, fences, and takes a ticket; the one that draws the last
 // ticket reads all partials back. Nothing waits on anything, so there is no spin to bound.
 #include <mutex>
+#include <vector>
 
 #include "glue.cuh"
 #include "kv_pool.h"
@@ -44,6 +45,9 @@ struct PaArgs {
   float scale;
   int* status;
   uint32_t* tickets;  // [seq][kv head], zero between calls; nullptr = separate stage-2 launch
+  // Chunked prefill: grid row `seq` is one query token; row_seq[seq] names the sequence whose
+  // block table it walks (nullptr: the row is the sequence, as in decode).
+  const uint32_t* row_seq;
   // Decode-step fusion (src/model.rs:1141-1207), off when k_new is nullptr: q arrives
   // un-rotated and is rotated as it is staged; the CTA whose partition holds the newest token
   // (position context_len - 1) rotates that token's K, quantises K and V and stores them in
@@ -145,10 +149,11 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
 
   // physical blocks of this partition (bounds-checked once); partitions start on a block
   const uint32_t nb = (n + bs - 1) / bs;
+  const uint32_t tseq = a.row_seq ? a.row_seq[seq] : seq;
   {
     const uint32_t first_blk = t0 / bs;
     for (uint32_t b = tid; b < nb; b += NT) {
-      uint32_t phys = a.tables[(size_t)seq * a.max_blocks + first_blk + b];
+      uint32_t phys = a.tables[(size_t)tseq * a.max_blocks + first_blk + b];
       if (phys >= a.g.num_blocks) {
         atomicOr(a.status, DEV_BAD_INDEX);
         phys = 0;
@@ -579,10 +584,27 @@ static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_
     launch_stage1_nt<G, PA_THREADS>(ctx, a, grid, smem);
 }
 
+int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                                    const float* q, const uint32_t* tables, const uint32_t* lens,
+                                    float* out, const kanso_paged_attention_params* p,
+                                    uint32_t max_ctx_hint, const PaDecodeFusion* fusion,
+                                    const uint32_t* row_seq);
+
 int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
                                const float* q, const uint32_t* tables, const uint32_t* lens,
                                float* out, const kanso_paged_attention_params* p,
                                uint32_t max_ctx_hint, const PaDecodeFusion* fusion) {
+  return launch_paged_attention_rows(ctx, kv, layer, q, tables, lens, out, p, max_ctx_hint,
+                                     fusion, nullptr);
+}
+
+// p->num_seqs is the number of grid rows (query tokens); with row_seq the block tables hold
+// one row per SEQUENCE and row_seq maps each grid row to its sequence.
+int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
+                                    const float* q, const uint32_t* tables, const uint32_t* lens,
+                                    float* out, const kanso_paged_attention_params* p,
+                                    uint32_t max_ctx_hint, const PaDecodeFusion* fusion,
+                                    const uint32_t* row_seq) {
   KvGeom g = kv_geom(kv);
   const uint32_t G = p->num_heads / p->num_kv_heads;
   const uint32_t hd = p->head_dim;
@@ -626,6 +648,7 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
   const bool merge_in_stage1 =
       (uint64_t)p->num_seqs * p->num_kv_heads <= kanso_cuda_ctx::kPaTickets && nparts <= pt;
   a.tickets = merge_in_stage1 ? ctx->pa_tickets : nullptr;
+  a.row_seq = row_seq;
   a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
   a.positions = a.slots = nullptr;
   a.table_len = 0;
@@ -711,6 +734,74 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
   }
   return launch_paged_attention(ctx, kv, layer, q, block_tables, context_lens, out, params,
                                 max_ctx, nullptr);
+}
+
+// Chunked-prefill attention: every query token of every sequence is one grid row whose context
+// is the prefix up to and including itself; the rows of a sequence share its block-table row.
+// The arithmetic per row is exactly the decode attention's (the reference adds -1e9 to the
+// masked scores, src/model.rs:1027-1043, which leaves exp() == 0 for them).
+int32_t kanso_cuda_paged_attention_prefill(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
+                                           uint32_t layer, const float* q,
+                                           const uint32_t* block_tables,
+                                           const uint32_t* host_context_lens,
+                                           const uint32_t* host_query_lens, float* out,
+                                           const kanso_paged_attention_params* params) {
+  if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "paged_attention_prefill: ctx is NULL");
+  char msg[256];
+  int32_t st = validate_params(params, msg, sizeof msg);
+  if (st) return fail(ctx, st, "%s", msg);
+  if (!kv || !q || !block_tables || !host_context_lens || !host_query_lens || !out)
+    return fail(ctx, KANSO_ERR_SHAPE, "paged_attention_prefill: NULL pointer");
+  if (layer >= kv->layers)
+    return fail(ctx, KANSO_ERR_SHAPE, "Layer index %u out of bounds (%u)", layer, kv->layers);
+  if (params->num_kv_heads != kv->kv_heads || params->head_dim != kv->head_dim ||
+      params->block_size != kv->block_size)
+    return fail(ctx, KANSO_ERR_SHAPE, "paged attention: params do not match the pool");
+  const uint32_t hd = params->head_dim;
+  if (hd < 16 || (hd & (hd - 1)) != 0)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                "paged attention: head_dim %u is not one of 16, 32, 64, 128, 256", hd);
+  const uint64_t cap = (uint64_t)params->max_num_blocks_per_seq * params->block_size;
+  std::vector<uint32_t> rows;  // [row_seq | row_ctx]
+  uint64_t T = 0;
+  for (uint32_t s = 0; s < params->num_seqs; ++s) T += host_query_lens[s];
+  if (T == 0) return fail(ctx, KANSO_ERR_SHAPE, "paged_attention_prefill: no query tokens");
+  if (T > (1u << 20))
+    return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged_attention_prefill: %llu query tokens",
+                (unsigned long long)T);
+  rows.resize(2 * T);
+  uint32_t max_ctx = 0;
+  uint64_t t = 0;
+  for (uint32_t s = 0; s < params->num_seqs; ++s) {
+    const uint32_t ql = host_query_lens[s], cl = host_context_lens[s];
+    // forward_batch_rows' checks (src/model.rs:1434-1455): the context includes the chunk
+    if (cl < ql || cl > cap)
+      return fail(ctx, KANSO_ERR_SHAPE,
+                  "paged_attention_prefill: sequence %u: context %u, %u query tokens, table "
+                  "capacity %llu", s, cl, ql, (unsigned long long)cap);
+    for (uint32_t i = 0; i < ql; ++i, ++t) {
+      rows[t] = s;
+      rows[T + t] = cl - ql + i + 1;  // query i sits at position cl - ql + i
+    }
+    if (cl > max_ctx) max_ctx = cl;
+  }
+  // one grid row per query token; the row arrays are stream-ordered temporaries
+  kanso_paged_attention_params pr = *params;
+  pr.num_seqs = (uint32_t)T;
+  if ((st = validate_params(&pr, msg, sizeof msg))) return fail(ctx, st, "%s", msg);
+  uint32_t* drows = nullptr;
+  KANSO_CUDA_TRY(ctx, cudaMallocAsync((void**)&drows, 2 * T * sizeof(uint32_t), ctx->stream),
+                 "paged_attention_prefill: row arrays");
+  cudaError_t ce = cudaMemcpyAsync(drows, rows.data(), 2 * T * sizeof(uint32_t),
+                                   cudaMemcpyHostToDevice, ctx->stream);
+  if (ce == cudaSuccess) {
+    st = launch_paged_attention_rows(ctx, kv, layer, q, block_tables, drows + T, out, &pr, max_ctx,
+                                     nullptr, drows);
+  } else {
+    st = cuda_fail(ctx, ce, "paged_attention_prefill: row arrays to device");
+  }
+  cudaFreeAsync(drows, ctx->stream);
+  return st;
 }
 
 }  // extern "C"
@@ -820,6 +911,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.scale = p->scale;
   a.status = ctx->dev_status;
   a.tickets = nullptr;  // two launches: stage 2 merges
+  a.row_seq = nullptr;
   a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
   a.positions = a.slots = nullptr;
   a.table_len = 0;

@@ -1,4 +1,6 @@
 // Device-resident weights and the Model::linear call on them.
+#include <atomic>
+#include <chrono>
 #include <cstring>
 
 #include "ctx.h"
@@ -78,6 +80,8 @@ int32_t kanso_cuda_weight_upload(kanso_cuda_ctx* ctx, const void* host_bytes, si
 int32_t kanso_cuda_weight_free(kanso_cuda_weight* w) {
   if (!w) return KANSO_OK;
   cudaDeviceSynchronize();  // the context may already be destroyed
+  for (auto& g : w->host_graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
   cudaFree(w->dev);
   delete w;
   return KANSO_OK;
@@ -92,11 +96,38 @@ int32_t kanso_cuda_linear(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const
   return matmul_dispatch(ctx, w->dtype, w->dev, x, y, M, w->rows, w->cols, act_mode);
 }
 
-int32_t kanso_cuda_linear_host(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
+// Model::linear with host activations. The first call of a (weight, M, mode) runs the plain
+// sequence: copy in, matmul, copy out, status word, wait. From the second call on the same
+// sequence is replayed as ONE captured graph launch (the staging addresses are fixed, the
+// matmul has already sized the context's scratch, so nothing allocates during the capture):
+// four driver calls and their gaps on the stream become one, which is most of what a host
+// call costs around a 10 us kernel. A capture that cannot be made (the caller is itself
+// capturing this stream, or the driver refuses) leaves the plain sequence in place.
+static int32_t linear_host_enqueue(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, char* ph,
+                                   char* pd, size_t xb, size_t xb_al, size_t yb, int64_t M,
+                                   int32_t act_mode) {
+  KANSO_CUDA_TRY(ctx, cudaMemcpyAsync(pd, ph, xb, cudaMemcpyHostToDevice, ctx->stream),
+                 "linear_host: activations to device");
+  int32_t st = matmul_dispatch(ctx, w->dtype, w->dev, (const float*)pd, (float*)(pd + xb_al), M,
+                               w->rows, w->cols, act_mode);
+  if (st) return st;
+  KANSO_CUDA_TRY(ctx,
+                 cudaMemcpyAsync(ph + xb_al, pd + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream),
+                 "linear_host: result to host");
+  KANSO_CUDA_TRY(ctx,
+                 cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int),
+                                 cudaMemcpyDeviceToHost, ctx->stream),
+                 "linear_host: status word");
+  return KANSO_OK;
+}
+
+int32_t kanso_cuda_linear_host(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w_in,
                                const float* x_host, float* y_host, int64_t M, int32_t act_mode) {
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "linear_host: ctx is NULL");
-  if (!w || !x_host || !y_host) return fail(ctx, KANSO_ERR_SHAPE, "linear_host: NULL pointer");
+  if (!w_in || !x_host || !y_host) return fail(ctx, KANSO_ERR_SHAPE, "linear_host: NULL pointer");
   if (M <= 0) return M == 0 ? KANSO_OK : fail(ctx, KANSO_ERR_SHAPE, "linear_host: M < 0");
+  // the handle caches its captured calls: the cache is bookkeeping, not part of the weight
+  kanso_cuda_weight* w = const_cast<kanso_cuda_weight*>(w_in);
   size_t xb = sizeof(float) * (size_t)M * w->cols, yb = sizeof(float) * (size_t)M * w->rows;
   size_t xb_al = (xb + 255) & ~size_t(255);
   int32_t st = ctx_pinned(ctx, xb_al + yb);
@@ -106,15 +137,71 @@ int32_t kanso_cuda_linear_host(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w,
   char* ph = (char*)ctx->pinned;
   char* pd = (char*)ctx->stage_dev;
   std::memcpy(ph, x_host, xb);
-  KANSO_CUDA_TRY(ctx, cudaMemcpyAsync(pd, ph, xb, cudaMemcpyHostToDevice, ctx->stream),
-                 "linear_host: activations to device");
-  st = matmul_dispatch(ctx, w->dtype, w->dev, (const float*)pd, (float*)(pd + xb_al), M, w->rows,
-                       w->cols, act_mode);
-  if (st) return st;
-  KANSO_CUDA_TRY(ctx,
-                 cudaMemcpyAsync(ph + xb_al, pd + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream),
-                 "linear_host: result to host");
-  st = kanso_cuda_sync(ctx);
+
+  kanso_host_graph* hg = nullptr;
+  for (auto& g : w->host_graphs)
+    if (g.M == M && g.act_mode == act_mode) hg = &g;
+  if (hg && (hg->buf_gen != ctx->buf_gen || hg->overlap != ctx->overlap_weight_prefetch)) {
+    if (hg->exec) cudaGraphExecDestroy(hg->exec);  // the staging buffers moved: capture again
+    *hg = kanso_host_graph{};
+    hg->M = -1;
+    hg = nullptr;
+  }
+  if (!hg && w->host_calls >= 1) {
+    // second call of this shape: the plain sequence has run once, capture it now
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cs) == cudaSuccess &&
+        cs == cudaStreamCaptureStatusNone) {
+      kanso_host_graph g;
+      g.M = M;
+      g.act_mode = act_mode;
+      g.buf_gen = ctx->buf_gen;
+      g.overlap = ctx->overlap_weight_prefetch;
+      const uint64_t launches0 = ctx->launches;
+      if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int32_t est = linear_host_enqueue(ctx, w, ph, pd, xb, xb_al, yb, M, act_mode);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ee = cudaStreamEndCapture(ctx->stream, &graph);
+        if (est == KANSO_OK && ee == cudaSuccess && graph && g.buf_gen == ctx->buf_gen &&
+            cudaGraphInstantiate(&g.exec, graph, 0) != cudaSuccess)
+          g.exec = nullptr;
+        if (est != KANSO_OK || ee != cudaSuccess || g.buf_gen != ctx->buf_gen) g.exec = nullptr;
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+      }
+      ctx->launches = launches0;  // nothing has run yet
+      // remember the kernels one replay stands for
+      w->host_graphs.push_back(g);
+      hg = &w->host_graphs.back();
+    }
+  }
+  w->host_calls++;
+  // The status word is the last thing the stream copies to the host. With a sentinel in its
+  // place the host can watch that pinned word instead of asking the driver: when it changes,
+  // the result (copied before it, on the same stream) has landed too.
+  volatile int* hs = ctx->host_status;
+  *hs = -1;
+  if (hg && hg->exec) {
+    KANSO_CUDA_TRY(ctx, cudaGraphLaunch(hg->exec, ctx->stream), "linear_host: graph launch");
+    ctx->launches += 1;  // at least the matmul kernel (its activation pack, if any, not counted)
+  } else {
+    st = linear_host_enqueue(ctx, w, ph, pd, xb, xb_al, yb, M, act_mode);
+    if (st) return st;
+  }
+  {
+    const auto t0 = std::chrono::steady_clock::now();
+    uint32_t spins = 0;
+    while (*hs == -1) {
+      if ((++spins & 0xFFFu) == 0 &&
+          std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(200)) {
+        // something is slow (or failed): let the driver wait and report
+        KANSO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream), "linear_host: wait");
+        break;
+      }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+  }
+  st = status_word_result(ctx);
   if (st) return st;
   std::memcpy(y_host, ph + xb_al, yb);
   return KANSO_OK;

@@ -595,6 +595,53 @@ int32_t kanso_ref_paged_attention_int8(const kanso_ref_kv* kv, uint32_t layer, c
   return ST_OK;
 }
 
+// Chunked-prefill attention of one sequence, as Model::forward_prefill does it
+// (src/model.rs:1027-1085 with gqa_attention, src/model.rs:764-795): gather the whole prefix
+// 0..start_pos+chunk_len from the pool (the chunk's own tokens were written just before), form
+// the score matrix [chunk_len, total_len] scaled by `scale`, ADD the offset causal mask (-1e9
+// where key j > start_pos + i), softmax over the row (max-subtracted), then P.V.
+int32_t kanso_ref_prefill_attention_int8(const kanso_ref_kv* kv, uint32_t layer, const float* q,
+                                         const uint32_t* blocks, uint32_t nblocks,
+                                         uint32_t start_pos, uint32_t chunk_len,
+                                         uint32_t num_heads, float scale, float* out) {
+  const uint32_t KH = kv->kv_heads, hd = kv->head_dim;
+  if (num_heads % KH != 0 || chunk_len == 0) return ST_SHAPE;
+  const uint32_t group = num_heads / KH, total = start_pos + chunk_len;
+  std::vector<float> kd((size_t)total * KH * hd), vd((size_t)total * KH * hd);
+  int32_t st = kanso_ref_kv_gather(kv, layer, blocks, nblocks, total, kd.data(), vd.data());
+  if (st != ST_OK) return st;
+  std::vector<float> sc(total);
+  for (uint32_t i = 0; i < chunk_len; ++i) {
+    for (uint32_t h = 0; h < num_heads; ++h) {
+      const uint32_t kvh = h / group;
+      const float* qv = q + ((size_t)i * num_heads + h) * hd;
+      float mx = -INFINITY;
+      for (uint32_t j = 0; j < total; ++j) {
+        const float* kr = kd.data() + ((size_t)j * KH + kvh) * hd;
+        float dot = 0.0f;
+        for (uint32_t d = 0; d < hd; ++d) dot += qv[d] * kr[d];
+        float v = dot * scale;
+        if (j > start_pos + i) v = v + -1e9f;
+        sc[j] = v;
+        mx = std::max(mx, v);
+      }
+      float sum = 0.0f;
+      for (uint32_t j = 0; j < total; ++j) {
+        sc[j] = std::exp(sc[j] - mx);
+        sum += sc[j];
+      }
+      float* o = out + ((size_t)i * num_heads + h) * hd;
+      for (uint32_t d = 0; d < hd; ++d) o[d] = 0.0f;
+      for (uint32_t j = 0; j < total; ++j) {
+        const float pj = sc[j] / sum;
+        const float* vr = vd.data() + ((size_t)j * KH + kvh) * hd;
+        for (uint32_t d = 0; d < hd; ++d) o[d] += pj * vr[d];
+      }
+    }
+  }
+  return ST_OK;
+}
+
 /* ------------------------------ glue ------------------------------ */
 
 // src/model.rs:653-659: x / sqrt(mean(x^2) + eps) * w

@@ -128,6 +128,15 @@ int32_t kanso_ref_paged_attention_int8(const kanso_ref_kv* kv, uint32_t layer, c
                                        const uint32_t* context_lens,
                                        const kanso_ref_pa_params* p, float* out);
 
+/* Chunked-prefill attention of one sequence as Model::forward_prefill computes it
+ * (src/model.rs:1027-1085, gqa_attention src/model.rs:764-795): the prefix 0..start_pos+chunk_len
+ * gathered from the int8 pool, an offset causal mask of -1e9 added to the scaled scores, softmax,
+ * P.V. q and out f32 [chunk_len, num_heads, head_dim]. */
+int32_t kanso_ref_prefill_attention_int8(const kanso_ref_kv* kv, uint32_t layer, const float* q,
+                                         const uint32_t* blocks, uint32_t nblocks,
+                                         uint32_t start_pos, uint32_t chunk_len,
+                                         uint32_t num_heads, float scale, float* out);
+
 /* ---- glue: src/model.rs:653-737,367-382; src/sampler.rs:7-17 ---- */
 void kanso_ref_rmsnorm(const float* x, const float* w, float* out, int64_t rows, int64_t hidden,
                        float eps);

@@ -323,6 +323,19 @@ def paged_attention_int8(pool: KvPool, layer, q, block_tables, context_lens, p: 
     return st, out
 
 
+def prefill_attention_int8(pool: KvPool, layer, q, blocks, start_pos, num_heads, scale):
+    """q f32 [chunk_len, num_heads*head_dim]; returns (status, out of the same shape)."""
+    q = _f32(q)
+    blocks = _u32(blocks)
+    chunk = q.shape[0]
+    out = np.empty_like(q)
+    st = lib().kanso_ref_prefill_attention_int8(pool.h, C.c_uint32(layer), _p(q), _p(blocks),
+                                                C.c_uint32(blocks.size), C.c_uint32(start_pos),
+                                                C.c_uint32(chunk), C.c_uint32(num_heads),
+                                                C.c_float(scale), _p(out))
+    return st, out
+
+
 # ----------------------------- glue -----------------------------
 def rmsnorm(x, w, eps):
     x, w = _f32(x), _f32(w)
