@@ -295,6 +295,17 @@ def gemm_legs(torch, kb, O, ctx, stream):
                 res[f"{name}_M{M}_N{rows}_K{K}"] = {
                     "us_per_call": us, "TFLOP/s": flops / us / 1e6, "GB/s": byts / us / 1e3,
                     "bound": bound, "frac_of_bound": frac}
+                if dtype == kb.DTYPE_Q8_0 and rows == 14336 and M in (32, 128):
+                    # the bit-exact mode: activations quantised per 32 (quantize_row_q8_0), int32
+                    # block sums on tcgen05 kind::i8
+                    def step_q8():
+                        for w_ in ws:
+                            f(w_, x, y, M, rows, K, kb.ACT_Q8)
+                    us8 = _graph_time_us(torch, stream, step_q8, copies, iters=5)
+                    ctx.sync()
+                    res[f"q8_0_act_q8_M{M}_N{rows}_K{K}"] = {
+                        "us_per_call": us8, "TOP/s": flops / us8 / 1e6, "GB/s": byts / us8 / 1e3,
+                        "frac_of_hbm": byts / us8 / 1e3 / hbm}
             del ws
     return res
 

@@ -533,6 +533,22 @@ static TmEncodeFn tm_encoder() {
   return fn;
 }
 
+// The tensor map of a block matrix [N][row_bytes] read in boxes of 128 rows x 128 bytes with
+// the 128-byte swizzle (shared with the int8 GEMM). KANSO_ERR_UNSUPPORTED: no encoder.
+int32_t tma_encode_weight_map(const void* w, int64_t row_bytes, int64_t N, CUtensorMap* map) {
+  TmEncodeFn encode = tm_encoder();
+  if (!encode) return KANSO_ERR_UNSUPPORTED;
+  const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
+  const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {TM_BOX_W, TM_TILE_N};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), gdim,
+                             gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return cr == CUDA_SUCCESS ? KANSO_OK : KANSO_ERR_DEVICE;
+}
+
 // y[M,N] = x[M,K] @ W^T for 9..512 activation rows. Sets *handled = false (and launches
 // nothing) when the shape is outside this kernel's range: rows of the block matrix must start
 // on 16-byte boundaries (every Q4_K matrix; Q8_0 when K % 256 == 0).

@@ -18,6 +18,8 @@ int32_t q8_mma_matmul(kanso_cuda_ctx* ctx, int nseg, const void* const* w, float
 
 int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
                    int64_t M, int64_t N, int64_t K, bool* handled);
+int32_t i8_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y, int64_t M,
+                  int64_t N, int64_t K, bool* handled);
 
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
@@ -48,6 +50,22 @@ int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const
                              K, &handled);
       if (st != KANSO_OK) return st;
       if (!handled) all = false;
+    }
+    if (all) return KANSO_OK;
+  }
+  // Q8_0 weights with Q8 activations and more than 8 rows: int8 tensor-core GEMM with exact
+  // int32 block sums, 128 rows per pass over the weights
+  if (M > 8 && act_mode == KANSO_ACT_Q8 && dtype == KANSO_DTYPE_Q8_0 && N > 0 && K > 0 && w && x &&
+      y) {
+    bool all = true;
+    for (int64_t m0 = 0; m0 < M && all;) {
+      int64_t mc = M - m0 < 128 ? M - m0 : 128;
+      if (M - m0 - mc > 0 && M - m0 - mc < 9) mc -= 16;  // a short tail rides with this chunk
+      bool handled = false;
+      int32_t st = i8_matmul(ctx, w, x + m0 * K, y + m0 * N, mc, N, K, &handled);
+      if (st != KANSO_OK) return st;
+      if (!handled) all = false;
+      m0 += mc;
     }
     if (all) return KANSO_OK;
   }

@@ -80,6 +80,28 @@ def test_q8_activation_mode_at_config_shapes(ctx, kb, oracle, torch_cuda, M):
     assert float(np.max(np.abs(got[:, pick] - ref))) / float(np.max(np.abs(got))) <= 1e-5
 
 
+@pytest.mark.parametrize("M", [16, 100, 128])
+def test_q8_activation_gemm_is_bit_exact_when_k_is_not_split(ctx, kb, oracle, torch_cuda, M):
+    """More than 8 rows in KANSO_ACT_Q8 mode run on tcgen05 kind::i8: the int32 block sums are
+    exact and the f32 scaling and additions follow scalar_dot_q8_0_q8_0 / scalar_gemv_q8_0
+    (src/quant/q8_0.rs:60-66,82-92) operation for operation, so on a matrix wide enough not to be
+    split along K (14336 rows = 112 CTAs) the result equals the oracle's bit for bit."""
+    torch = torch_cuda
+    N = 14336
+    rows2d, W = quantized(oracle, kb, ctx, "q8_0", N)
+    rng = np.random.Generator(np.random.PCG64(0xB2000340 + M))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    W.forward(dev(torch, x), y, M, kb.ACT_Q8)
+    ctx.sync()
+    got = y.cpu().numpy()
+    pick = sample_rows(rng, N)
+    ref = oracle.gemm_q8_0(np.ascontiguousarray(rows2d[pick]).reshape(-1), x, M, pick.size, K,
+                           oracle.ACT_Q8)
+    assert np.isfinite(got).all()
+    assert np.array_equal(got[:, pick], ref)
+
+
 def test_q8_0_gemv_1024_against_dense(ctx, kb, oracle, torch_cuda):
     """The reference's own 1024 x 1024 case at its own size and bound: closed-form int8 pattern,
     d = 0.015, x = sin(0.02 i), every row within 1e-2 (absolute) of the dense f32 product
