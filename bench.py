@@ -36,7 +36,7 @@ Q4K_BYTES, QK_K = 144, 256
 SEED = 0xB2000000 + 2 * 100
 # dram__bytes_read + dram__bytes_write of one launch of the headline kernel on the 14336 x 4096
 # matrix: the mean of the two launches of the ncu capture summarised under profiles/
-NCU_DRAM_BYTES_PER_LAUNCH = 33_102_080
+NCU_DRAM_BYTES_PER_LAUNCH = 33_110_016
 
 
 def alg_bytes(rows, cols):
@@ -946,7 +946,7 @@ def main():
                     help="time only the decode step at these batch sizes (1 GPU) and print them; "
                          "for profiler captures of that path")
     ap.add_argument("--gemm-only", default=None, metavar="FMT,M",
-                    help="run only the cfg 3 GEMM (q8_0 or q4_k, N=14336, K=4096) with M activation "
+                    help="run only the cfg 3 GEMM (q8_0, q4_k, or q8_0_q8 for Q8 activations; N=14336, K=4096) with M activation "
                          "rows over four weight copies, eagerly; for profiler captures of that path")
     args = ap.parse_args()
     if args.gemm_only:
@@ -958,13 +958,15 @@ def main():
         ctx = kb.Context(0, stream)
         fmt, M = args.gemm_only.split(",")
         M = int(M)
+        act = kb.ACT_Q8 if fmt.endswith("_q8") else kb.ACT_F32  # q8_0_q8: Q8 activations
+        fmt = fmt[:-3] if fmt.endswith("_q8") else fmt
         dtype = kb.DTYPE_Q8_0 if fmt == "q8_0" else kb.DTYPE_Q4_K
         ws = _random_blocks(torch, kb, dtype, 14336, 4096, 4)
         x = torch.randn(M, 4096, device="cuda")
         y = torch.empty(M, 14336, device="cuda")
         for w in ws:
             (ctx.gemm_q8_0 if dtype == kb.DTYPE_Q8_0 else ctx.gemm_q4_k)(w, x, y, M, 14336, 4096,
-                                                                         kb.ACT_F32)
+                                                                         act)
         ctx.sync()
         print(json.dumps({"gemm_only": args.gemm_only, "launches": int(ctx.launches)}))
         return
