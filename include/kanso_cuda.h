@@ -324,7 +324,11 @@ uint64_t kanso_cuda_kv_bytes_per_token(const kanso_cuda_kv* kv);
  * block_tables u32[num_seqs*max_blocks], context_lens u32[num_seqs],
  * out f32[num_seqs, num_heads*head_dim]; all device. host_context_lens (optional)
  * enables the reference's host checks: ctx 0 and ctx > capacity are rejected
- * (paged_attention.rs:343-355). */
+ * (paged_attention.rs:343-355). head_dim must be a power of two from 16 to 256 (the reference's
+ * validation only asks for 1..256 and a whole GQA ratio, paged_attention.rs:24-82; its presets use
+ * 64 and 128): any other value returns KANSO_ERR_UNSUPPORTED. A device context length beyond
+ * the table capacity or beyond the host's figure is cut off there and reported as
+ * KANSO_ERR_SHAPE by the next kanso_cuda_sync. */
 int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
                                    const float* q, const uint32_t* block_tables,
                                    const uint32_t* context_lens, float* out,

@@ -4,22 +4,29 @@
 //
 //   y[M,N] = x[M,K] @ W[N,K]^T,  W in GGUF Q8_0 / Q4_K blocks, x and y f32.
 //
+// This is the three-product form used by the decode step's chain of matmuls (more than 8
+// sequences) and by shapes whose rows do not start on 16-byte boundaries; single matmuls of 9..512
+// rows with aligned rows take the TMA-staged kernel in gemm_tma.cu, KANSO_ACT_Q8 batches the
+// kind::i8 kernel in gemm_i8.cu.
+//
 // Mapping. The weight matrix is the 128-row operand of the MMA (A, K-major) and the
-// activations are the narrow operand (B, K-major, 16..256 rows), so one CTA owns 128 weight
+// activations are the narrow operand (B, K-major, 16..128 rows), so one CTA owns 128 weight
 // rows x one K range and streams its weight bytes from HBM exactly once:
-//   * a small pre-pass converts x to f16 in the canonical K-major core-matrix layout, one
-//     contiguous tile per 64-wide K stage, so every CTA fetches its B tiles with plain
-//     128-bit copies out of L2;
-//   * per stage (64 values of K) the CTA's warps read the quantized blocks of its 128 rows
-//     straight from global memory, dequantise in registers (Q8_0: exact int8 -> f16 by byte
-//     permute, one rounding in d*q; Q4_K: (d*sc)*q - dmin*m in f32, one rounding to f16) and
-//     store 16-byte core-matrix rows into shared memory (no swizzle: 8 rows x 16 bytes per
-//     core matrix, K-adjacent matrices 2 KB apart), double-buffered;
-//   * one elected thread issues four tcgen05.mma (M=128, N=Mt, K=16, kind::f16, f32
-//     accumulate in TMEM) per stage and commits them to an mbarrier, which frees the stage;
-//   * after the last stage four warps read the accumulator with tcgen05.ld (lane = weight
-//     row, column = activation row) and write y; with split-K the partial sums are added
-//     with red.global (y is cleared first).
+//   * a pack kernel converts x to f16 hi/lo planes in the canonical K-major core-matrix layout,
+//     one contiguous tile per 64-wide K stage (it can fold in rmsnorm or the SwiGLU product and
+//     clears the outputs of a split-K launch);
+//   * 16 producer warps copy the raw block bytes of the CTA's 128 rows into a shared-memory ring
+//     with cp.async (three stages ahead), dequantise 16 weights per thread and stage (Q8_0: exact
+//     int8 -> f16 by byte permute; Q4_K: (d*sc)*q - dmin*m in f32) into f16 hi/lo terms and store
+//     16-byte core-matrix rows (no swizzle: 8 rows x 16 bytes per core matrix, K-adjacent matrices
+//     2 KB apart), double-buffered;
+//   * a 17th warp fetches the activation tile of the stage with one cp.async.bulk, and its
+//     elected lane issues the tcgen05.mma instructions (M=128, N=Mt, K=16, kind::f16, f32
+//     accumulate in TMEM) and commits them to per-buffer mbarriers, which frees the stage;
+//   * after the last stage the producer warps read the accumulator with tcgen05.ld (lane = weight
+//     row, column = activation row) and write y (optionally adding a residual); with split-K the
+//     partial sums are added with atomics (y is cleared by the pack kernel).
+// Several matrices that share their activations (Q/K/V, gate/up) run as one launch.
 // Every mbarrier wait is bounded; on a timeout the CTA records DEV_WAIT_TIMEOUT, frees its
 // TMEM columns and returns.
 //
@@ -27,8 +34,7 @@
 // the 1e-3 bound but drifts past the 1e-2 logit bound over a stack of layers, so both
 // operands are split in two f16 terms, w = wh + wl and x = xh + xl (the remainders are exact
 // or near-exact), and each 16-wide K step issues three MMAs: wh*xh + wl*xh + wh*xl. Only the
-// wl*xl term (2^-22) is dropped; products accumulate in f32 in TMEM. KANSO_ACT_Q8 (bit-exact int32 block sums) is not offered on this path: its
-// per-32 scales would force the accumulator out of TMEM every K=32.
+// wl*xl term (2^-22) is dropped; products accumulate in f32 in TMEM.
 #include <cstdlib>
 
 #include "ctx.h"

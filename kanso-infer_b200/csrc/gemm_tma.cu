@@ -36,6 +36,7 @@
 #include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up through the runtime
 
 #include <mutex>
+#include <type_traits>
 
 #include "ctx.h"
 #include "tc05.cuh"
@@ -142,102 +143,119 @@ __device__ __forceinline__ const uint8_t* tm_chunk(const uint8_t* slot, int row,
   return slot + row * TM_BOX_W + ((chunk ^ (row & 7)) << 4);
 }
 
-// Q8_0: this thread's chunk (16 stream bytes of its row) -> 16 f16 values d*q in the A tile.
-// `idx` counts boxes from the first one this CTA loaded (ring position), `box` is the box's
-// index in the row stream. A block's scale always precedes its values in the stream, at most
-// 33 bytes back: in this box or in the one before it, which is still in the ring.
-__device__ __forceinline__ void tm_dequant_q8_0(const uint8_t* Raw, int idx, int box, int cib,
-                                                int c, int row, uint8_t* Ab) {
-  const uint8_t* slot = Raw + (idx % TM_RAW_SLOTS) * TM_BOX;
-  const uint4 v = *reinterpret_cast<const uint4*>(tm_chunk(slot, row, cib));
-  const uint32_t o = (uint32_t)box * TM_BOX_W + (uint32_t)cib * 16u;  // warp-uniform
-  const uint32_t blk = o / 34u, within0 = o - 34u * blk;              // within0 is even
-  // byte pairs [0, s) of the chunk lie in block blk, pair s (if any) is the scale of block
-  // blk + 1, the pairs after it are that block's values
-  const uint32_t s = min(8u, (34u - within0) >> 1);
-  __half2 da = __float2half2_rn(0.f), db = da;
-  if (within0 != 0) {  // the scale of block blk sits before this chunk
-    const uint32_t od = 34u * blk, bd = od >> 7, in_box = od & 127u;
-    const uint8_t* sd = Raw + ((idx - (int)((uint32_t)box - bd)) % TM_RAW_SLOTS) * TM_BOX;
-    da = __half2half2(*reinterpret_cast<const __half*>(tm_chunk(sd, row, in_box >> 4) +
-                                                       (in_box & 15u)));
+// Broadcasts the low (HI = 0) or high (HI = 1) 16 bits of a word into both halves.
+template <int HI>
+__device__ __forceinline__ __half2 tm_bcast_half(uint32_t w) {
+  return u32_as_h2(__byte_perm(w, w, HI ? 0x3232 : 0x1010));
+}
+
+// Q8_0: 32 consecutive stream bytes of this thread's row (chunks 2c and 2c+1 of the box) -> two
+// k-steps of 16 f16 values d*q in the A tile. W0 = offset of the first of those bytes inside its
+// 34-byte block: even, 0..32, and a compile-time constant, because the 17 possible phases are
+// dispatched by a switch in the caller: which byte pair holds a scale and which scale every other
+// pair takes is then known to the compiler and costs no instruction. A pair that holds a scale's
+// own bytes is converted like any other: its activation is zero in the packed stream, and the
+// product of two finite f16 numbers with zero is zero.
+//   W0 == 0 : pair 0 is the scale of the block the 15 pairs after it belong to;
+//   W0 == 2 : all 16 pairs belong to the block whose scale sits 2 bytes before them;
+//   W0 >= 4 : pairs [0, SB) belong to the block whose scale sits W0 bytes back, pair
+//             SB = 17 - W0/2 is the next block's scale, the pairs after it are that block's.
+// A scale that precedes the 32 bytes lies at most 32 bytes back: in this box (`cur`) or, for the
+// first two chunks of a box, in the one before it (`prev`), which is still in the ring.
+template <int W0>
+__device__ __forceinline__ void tm_dequant_q8_0(const uint8_t* cur, const uint8_t* prev, int c,
+                                                uint32_t row_off, uint32_t rsw, uint8_t* dst) {
+  constexpr int SB = W0 == 0 ? 0 : 17 - W0 / 2;
+  const uint8_t* rb = cur + row_off;
+  const uint4 v0 = *reinterpret_cast<const uint4*>(rb + ((((uint32_t)(2 * c)) ^ rsw) << 4));
+  const uint4 v1 = *reinterpret_cast<const uint4*>(rb + ((((uint32_t)(2 * c + 1)) ^ rsw) << 4));
+  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  __half2 da, db;
+  if (W0 == 0) {
+    da = tm_bcast_half<0>(w[0]);
+    db = da;
+  } else {
+    const uint32_t bo = (uint32_t)(32 * c - W0) & 127u;  // warp-uniform
+    const uint8_t* src = (32 * c < W0 ? prev : cur) + row_off;
+    const unsigned short bits =
+        *reinterpret_cast<const unsigned short*>(src + ((((bo >> 4) ^ rsw) << 4) | (bo & 15u)));
+    da = __half2half2(__ushort_as_half(bits));
+    db = SB <= 15 ? tm_bcast_half<SB & 1>(w[(SB <= 15 ? SB : 0) >> 1]) : da;
   }
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  if (within0 == 0) {  // pair 0 is the scale of block blk itself
-    da = __half2half2(__ushort_as_half((unsigned short)(v.x & 0xFFFFu)));
-  } else if (s < 8) {
-    const uint32_t si = s >> 1;
-    const uint32_t ws = si == 0 ? v.x : si == 1 ? v.y : si == 2 ? v.z : v.w;
-    db = __half2half2(__ushort_as_half((unsigned short)((s & 1) ? (ws >> 16) : (ws & 0xFFFFu))));
-  }
-  const __half2 zero2 = __float2half2_rn(0.f);
   const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 + 128, exact in f16
-  uint32_t out[8];
+  uint32_t out[16];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 8; ++i) {
     const uint32_t q = w[i] ^ 0x80808080u;
     // 0x6400 | byte = 1024 + (q + 128) as f16, exactly
     const __half2 q01 = __hsub2(u32_as_h2(__byte_perm(q, 0x64646464u, 0x4140)), bias);
     const __half2 q23 = __hsub2(u32_as_h2(__byte_perm(q, 0x64646464u, 0x4342)), bias);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t p = 2 * i + h;  // byte pair of the chunk
-      __half2 d2;
-      if (p < s)
-        d2 = (p == 0 && within0 == 0) ? zero2 : da;  // a scale's own bytes count as zero
-      else
-        d2 = p == s ? zero2 : db;
-      out[p] = h2_as_u32(__hmul2(h ? q23 : q01, d2));
-    }
+    out[2 * i] = h2_as_u32(__hmul2(q01, (2 * i < SB) ? da : db));
+    out[2 * i + 1] = h2_as_u32(__hmul2(q23, (2 * i + 1 < SB) ? da : db));
   }
-  uint8_t* dst = Ab + (2 * c) * (TM_TILE_N * 16) + row * 16;
-  *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
-  *reinterpret_cast<uint4*>(dst + TM_TILE_N * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(dst + j * (TM_TILE_N * 16)) =
+        make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+}
+
+// Scale or minimum `j` (0..7) of a Q4_K header from the three words of its 12 packed bytes
+// (get_scale_min_k4, src/quant/q4_k.rs:13-28); j is a compile-time constant.
+template <int J, bool MIN>
+__device__ __forceinline__ uint32_t tm_k4_field(uint32_t y, uint32_t z, uint32_t w) {
+  if constexpr (J < 4) {
+    return ((MIN ? z : y) >> (8 * J)) & 63u;
+  } else {
+    const uint32_t lo = (w >> (8 * (J - 4) + (MIN ? 4 : 0))) & 0xFu;
+    const uint32_t hi = ((MIN ? z : y) >> (8 * (J - 4) + 6)) & 3u;
+    return lo | (hi << 4);
+  }
 }
 
 // Q4_K: this thread's nibble chunk -> two k-steps of 16 f16 values (low nibbles = sub-block 2g,
 // high nibbles = sub-block 2g+1 of the chunk's 64-weight group). w = d1*(q-8) - (m1 - 8*d1) with
 // d1 = d*sc, m1 = dmin*m (src/quant/q4_k.rs:30-55): centred on 8 so that the two f16 factors
-// carry a small constant instead of one the size of the weight range.
-__device__ __forceinline__ void tm_dequant_q4_k(const uint8_t* Raw, int idx, int box, int cib,
-                                                int c, int row, uint8_t* Ab) {
-  const uint32_t o = (uint32_t)box * TM_BOX_W + (uint32_t)cib * 16u;  // warp-uniform
-  const uint32_t sb = o / 144u, rem = o - 144u * sb;
-  if (rem == 0) return;  // header chunk: the MMA issuer skips its two k-steps
-  const uint32_t i = (rem >> 4) - 1u;
-  const uint8_t* slot = Raw + (idx % TM_RAW_SLOTS) * TM_BOX;
-  const uint4 qv = *reinterpret_cast<const uint4*>(tm_chunk(slot, row, cib));
-  // the super-block's header: at most 128 bytes back, in this box or the one before it
-  const uint32_t oh = 144u * sb, bh = oh >> 7;
-  const uint8_t* sh = Raw + ((idx - (int)((uint32_t)box - bh)) % TM_RAW_SLOTS) * TM_BOX;
-  const uint4 hdr = *reinterpret_cast<const uint4*>(tm_chunk(sh, row, (oh & 127u) >> 4));
+// carry a small constant instead of one the size of the weight range. CM = the chunk's index
+// inside its 144-byte super-block (1..8; 0 is the header chunk, which produces nothing), a
+// compile-time constant dispatched by a switch in the caller: the group, its two scale fields
+// and the header's distance are then fixed. The header lies CM chunks back: in this box or in
+// the one before it.
+template <int CM>
+__device__ __forceinline__ void tm_dequant_q4_k(const uint8_t* cur, const uint8_t* prev, int cib,
+                                                uint32_t row_off, uint32_t rsw, uint8_t* dst) {
+  constexpr int G = (CM - 1) >> 1;  // 64-weight group; sub-blocks 2G (low) and 2G+1 (high)
+  const uint4 qv = *reinterpret_cast<const uint4*>(cur + row_off + ((((uint32_t)cib) ^ rsw) << 4));
+  const uint32_t hc = (uint32_t)(cib - CM) & 7u;  // warp-uniform
+  const uint4 hdr = *reinterpret_cast<const uint4*>((cib < CM ? prev : cur) + row_off +
+                                                    ((hc ^ rsw) << 4));
   const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
-  uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
-  unpack_scales_k4(hdr.y, hdr.z, hdr.w, sc_lo, sc_hi, mn_lo, mn_hi);
-  const uint32_t g = i >> 1;  // 64-weight group; sub-blocks 2g (low) and 2g+1 (high)
-  const uint32_t scw = g < 2 ? sc_lo : sc_hi, mnw = g < 2 ? mn_lo : mn_hi;
-  const uint32_t sh0 = 16u * (g & 1u);
-  const float d1l = d * (float)((scw >> sh0) & 0xFFu), d1h = d * (float)((scw >> (sh0 + 8)) & 0xFFu);
-  const float m1l = dmin * (float)((mnw >> sh0) & 0xFFu);
-  const float m1h = dmin * (float)((mnw >> (sh0 + 8)) & 0xFFu);
+  const float d1l = d * (float)tm_k4_field<2 * G, false>(hdr.y, hdr.z, hdr.w);
+  const float d1h = d * (float)tm_k4_field<2 * G + 1, false>(hdr.y, hdr.z, hdr.w);
+  const float m1l = dmin * (float)tm_k4_field<2 * G, true>(hdr.y, hdr.z, hdr.w);
+  const float m1h = dmin * (float)tm_k4_field<2 * G + 1, true>(hdr.y, hdr.z, hdr.w);
   const __half2 dl2 = __float2half2_rn(d1l), dh2 = __float2half2_rn(d1h);
   const __half2 cl2 = __float2half2_rn(8.0f * d1l - m1l), ch2 = __float2half2_rn(8.0f * d1h - m1h);
-  const __half2 bias = __floats2half2_rn(1032.f, 1032.f);  // 1024 + 8
+  // low nibble: 0x6400 | q = 1024 + q; high nibble left in place: 0x6400 | 16q = 1024 + 16q, and
+  // (1024 + 16q) / 16 - 72 = q - 8 in one exact fused multiply-add
+  const __half2 bias = __floats2half2_rn(1032.f, 1032.f);
+  const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+  const __half2 m72 = __floats2half2_rn(-72.f, -72.f);
   const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
   uint32_t lo[8], hi[8];
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    // 0x6400 | nibble = 1024 + q as f16; pairs (byte 0, byte 2) and (byte 1, byte 3)
-    const uint32_t t0 = (w[k] & 0x000F000Fu) | 0x64006400u;
-    const uint32_t t1 = ((w[k] >> 4) & 0x000F000Fu) | 0x64006400u;
-    const uint32_t t2 = ((w[k] >> 8) & 0x000F000Fu) | 0x64006400u;
-    const uint32_t t3 = ((w[k] >> 12) & 0x000F000Fu) | 0x64006400u;
-    lo[2 * k] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t0), bias), dl2, cl2));
-    lo[2 * k + 1] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t2), bias), dl2, cl2));
-    hi[2 * k] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t1), bias), dh2, ch2));
-    hi[2 * k + 1] = h2_as_u32(__hfma2(__hsub2(u32_as_h2(t3), bias), dh2, ch2));
+    // pairs (byte 0, byte 2) and (byte 1, byte 3) of the word
+    const uint32_t w8 = w[k] >> 8;
+    const __half2 l0 = __hsub2(u32_as_h2((w[k] & 0x000F000Fu) | 0x64006400u), bias);
+    const __half2 h0 = __hfma2(u32_as_h2((w[k] & 0x00F000F0u) | 0x64006400u), sixteenth, m72);
+    const __half2 l1 = __hsub2(u32_as_h2((w8 & 0x000F000Fu) | 0x64006400u), bias);
+    const __half2 h1 = __hfma2(u32_as_h2((w8 & 0x00F000F0u) | 0x64006400u), sixteenth, m72);
+    lo[2 * k] = h2_as_u32(__hfma2(l0, dl2, cl2));
+    lo[2 * k + 1] = h2_as_u32(__hfma2(l1, dl2, cl2));
+    hi[2 * k] = h2_as_u32(__hfma2(h0, dh2, ch2));
+    hi[2 * k + 1] = h2_as_u32(__hfma2(h1, dh2, ch2));
   }
-  uint8_t* dst = Ab + (4 * c) * (TM_TILE_N * 16) + row * 16;  // k-steps 2c (low) and 2c+1 (high)
+  // k-steps 2c (low) and 2c+1 (high) of the stage
   *reinterpret_cast<uint4*>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   *reinterpret_cast<uint4*>(dst + TM_TILE_N * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
   *reinterpret_cast<uint4*>(dst + 2 * TM_TILE_N * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
@@ -333,26 +351,55 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
   pdl_launch_dependents();
 
   if (warp < TM_PRODUCERS / 32) {
-    const int row = tid & 127, c = tid >> 7;  // c: chunk within a group of four, warp-uniform
+    const int row = tid & 127, c = tid >> 7;  // c: quarter of the stage's chunks, warp-uniform
+    const uint32_t row_off = (uint32_t)row * TM_BOX_W, rsw = (uint32_t)row & 7u;
     int abuf = 0;
     uint32_t a_par = 1;  // parity that an unused a_empty barrier already satisfies
-    for (int box = first, idx = 0; box < b1; ++box, ++idx) {
-      if (!tm_warp_wait(&raw_full[idx % TM_RAW_SLOTS], (uint32_t)(idx / TM_RAW_SLOTS) & 1u, lane))
-        *abort_flag = 1;
+    int slot = 0, prev_slot = 0;
+    uint32_t raw_par = 0;
+    // Q8_0: phase of this thread's 32 bytes inside the 34-byte blocks, (128*box + 32*c) % 34 / 2;
+    // Q4_K: index of this thread's chunk inside the 9-chunk super-blocks, (8*box + c) % 9
+    uint32_t ph = FMT == TM_FMT_Q8_0 ? (uint32_t)((64 * (int64_t)first + 16 * c) % 17)
+                                     : (uint32_t)((8 * (int64_t)first + c) % 9);
+    for (int box = first; box < b1; ++box) {
+      if (!tm_warp_wait(&raw_full[slot], raw_par, lane)) *abort_flag = 1;
       if (*abort_flag) break;
+      const uint8_t* cur = Raw + slot * TM_BOX;
+      const uint8_t* prev = Raw + prev_slot * TM_BOX;
       if (box >= b0) {
 #pragma unroll 1
         for (int st = 0; st < SPB; ++st) {
           if (!tm_warp_wait(&a_empty[abuf], a_par, lane)) *abort_flag = 1;
           if (*abort_flag) break;
-          uint8_t* Ab = As + abuf * TM_A_STAGE;
-#pragma unroll
-          for (int j = 0; j < CH / 4; ++j) {
-            const int kc = 4 * j + c;  // chunk of the stage
-            if (FMT == TM_FMT_Q8_0)
-              tm_dequant_q8_0(Raw, idx, box, st * CH + kc, kc, row, Ab);
-            else
-              tm_dequant_q4_k(Raw, idx, box, st * CH + kc, kc, row, Ab);
+          uint8_t* dst = As + abuf * TM_A_STAGE + c * (4 * TM_TILE_N * 16) + row * 16;
+          if (FMT == TM_FMT_Q8_0) {
+            switch (ph) {
+#define TM_Q8_CASE(P) \
+  case P:             \
+    tm_dequant_q8_0<2 * P>(cur, prev, c, row_off, rsw, dst); \
+    break;
+              TM_Q8_CASE(0) TM_Q8_CASE(1) TM_Q8_CASE(2) TM_Q8_CASE(3) TM_Q8_CASE(4) TM_Q8_CASE(5)
+              TM_Q8_CASE(6) TM_Q8_CASE(7) TM_Q8_CASE(8) TM_Q8_CASE(9) TM_Q8_CASE(10)
+              TM_Q8_CASE(11) TM_Q8_CASE(12) TM_Q8_CASE(13) TM_Q8_CASE(14) TM_Q8_CASE(15)
+              TM_Q8_CASE(16)
+#undef TM_Q8_CASE
+              default:
+                break;
+            }
+          } else {
+            const int cib = st * CH + c;
+            switch (ph) {
+#define TM_Q4_CASE(P) \
+  case P:             \
+    tm_dequant_q4_k<P>(cur, prev, cib, row_off, rsw, dst); \
+    break;
+              TM_Q4_CASE(1) TM_Q4_CASE(2) TM_Q4_CASE(3) TM_Q4_CASE(4) TM_Q4_CASE(5) TM_Q4_CASE(6)
+              TM_Q4_CASE(7) TM_Q4_CASE(8)
+#undef TM_Q4_CASE
+              default:  // 0: the header chunk; the MMA issuer skips its two k-steps
+                break;
+            }
+            ph = ph >= 5u ? ph - 5u : ph + 4u;  // four chunks on, modulo 9
           }
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
           __syncwarp();
@@ -360,10 +407,18 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
           abuf ^= 1;
           if (abuf == 0) a_par ^= 1u;
         }
+      } else if (FMT == TM_FMT_Q4_K) {
+        ph = ph == 0u ? 8u : ph - 1u;  // a box that is only read for its headers: eight chunks on
       }
+      if (FMT == TM_FMT_Q8_0) ph = ph >= 4u ? ph - 4u : ph + 13u;  // 128 bytes on, modulo 34
       // the box before this one is no longer needed (scales and headers reach one box back)
       __syncwarp();
-      if (idx >= 1 && lane == 0) mbar_arrive(&raw_empty[(idx - 1) % TM_RAW_SLOTS]);
+      if (box > first && lane == 0) mbar_arrive(&raw_empty[prev_slot]);
+      prev_slot = slot;
+      if (++slot == TM_RAW_SLOTS) {
+        slot = 0;
+        raw_par ^= 1u;
+      }
     }
   } else if (warp == TM_PRODUCERS / 32) {
     // ---- MMA issuer: one thread, and every instruction it executes sits on the critical
@@ -385,41 +440,89 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       int abuf = 0;
       uint32_t a_par = 0;
       bool ok = true;
+      const uint32_t adesc_hi = (uint32_t)(adesc_buf0 >> 32), bdesc_hi = (uint32_t)(bdesc_base >> 32);
+      const uint32_t adesc_lo0 = (uint32_t)adesc_buf0, bdesc_lo0 = (uint32_t)bdesc_base;
       for (int ss = SPB * (b1 - b0); ss > 0 && ok; --ss) {
         if (!mbar_wait_bounded(&a_full[abuf], a_par)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        uint64_t adesc = adesc_buf0 + (uint64_t)((uint32_t)abuf * (TM_A_STAGE >> 4));
+        if (o + CH * 16u <= row_bytes && in_grp == 0) {
+          // ---- a stage whose chunks all lie inside the row (every stage but the tail of a row
+          // whose length is not a multiple of the box): straight-line code per slot size, every
+          // descriptor a constant offset from the stage's first ----
+          const uint32_t alo = adesc_lo0 + (uint32_t)abuf * (TM_A_STAGE >> 4);
+          const uint32_t hdr = FMT == TM_FMT_Q4_K ? (cm == 0u ? 0u : 9u - cm) : 99u;  // chunk to skip
+          auto run = [&](auto ub_tag) {
+            constexpr int UB = decltype(ub_tag)::value;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const bool valid = o < row_bytes && (FMT == TM_FMT_Q8_0 || cm != 0);
-#pragma unroll
-          for (int ks = 0; ks < UPC; ++ks) {
-            if (in_grp == 0) {
+            for (int g = 0; g < CH * UPC / UB; ++g) {
               if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
               tc_fence_after();
-              bdesc = bdesc_base + (uint64_t)(bslot * b_slot);
-            }
-            if (valid && ok) {
-              tc_mma_f16(tmem_base, adesc, bdesc, idesc0, acc);
-              if (two) tc_mma_f16(tmem_base + 256u, adesc, bdesc + 256u, idesc1, acc);
-              acc = 1;
-            }
-            adesc += a_kstep;
-            bdesc += b_unit;
-            if (++in_grp == ub) {
+              uint32_t blo = bdesc_lo0 + bslot * b_slot;
+#pragma unroll
+              for (int u = 0; u < UB; ++u) {
+                const int ks = g * UB + u;
+                const bool skip = FMT == TM_FMT_Q4_K && (uint32_t)(ks / UPC) == hdr;
+                if (!skip && ok) {
+                  const uint64_t ad = tc_desc_join(alo + (uint32_t)ks * a_kstep, adesc_hi);
+                  const uint64_t bd = tc_desc_join(blo, bdesc_hi);
+                  tc_mma_f16(tmem_base, ad, bd, idesc0, acc);
+                  if (UB == 1 && two)
+                    tc_mma_f16(tmem_base + 256u, ad, tc_desc_join(blo + 256u, bdesc_hi), idesc1, acc);
+                  acc = 1;
+                }
+                blo += b_unit;
+              }
               tc_commit(&b_empty[bslot]);
-              in_grp = 0;
               if (++bslot == TM_B_SLOTS) {
                 bslot = 0;
                 b_par ^= 1u;
               }
             }
+          };
+          if (ub == 8u)
+            run(std::integral_constant<int, 8>{});
+          else if (ub == 4u)
+            run(std::integral_constant<int, 4>{});
+          else if (ub == 2u)
+            run(std::integral_constant<int, 2>{});
+          else
+            run(std::integral_constant<int, 1>{});
+          o += CH * 16u;
+          if (FMT == TM_FMT_Q4_K) cm = cm >= 5u ? cm - 5u : cm + 4u;
+        } else {
+          uint64_t adesc = adesc_buf0 + (uint64_t)((uint32_t)abuf * (TM_A_STAGE >> 4));
+#pragma unroll 1
+          for (int c = 0; c < CH; ++c) {
+            const bool valid = o < row_bytes && (FMT == TM_FMT_Q8_0 || cm != 0);
+#pragma unroll 1
+            for (int ks = 0; ks < UPC; ++ks) {
+              if (in_grp == 0) {
+                if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
+                tc_fence_after();
+                bdesc = bdesc_base + (uint64_t)(bslot * b_slot);
+              }
+              if (valid && ok) {
+                tc_mma_f16(tmem_base, adesc, bdesc, idesc0, acc);
+                if (two) tc_mma_f16(tmem_base + 256u, adesc, bdesc + 256u, idesc1, acc);
+                acc = 1;
+              }
+              adesc += a_kstep;
+              bdesc += b_unit;
+              if (++in_grp == ub) {
+                tc_commit(&b_empty[bslot]);
+                in_grp = 0;
+                if (++bslot == TM_B_SLOTS) {
+                  bslot = 0;
+                  b_par ^= 1u;
+                }
+              }
+            }
+            o += 16u;
+            if (FMT == TM_FMT_Q4_K) cm = cm == 8u ? 0u : cm + 1u;
           }
-          o += 16u;
-          if (FMT == TM_FMT_Q4_K) cm = cm == 8u ? 0u : cm + 1u;
         }
         tc_commit(&a_empty[abuf]);
         abuf ^= 1;
