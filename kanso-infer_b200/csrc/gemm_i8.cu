@@ -127,10 +127,11 @@ __device__ __forceinline__ bool i8_wait_polite(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// Every lane polls, so that the warp stays converged through the wait (a poll loop entered by
+// lane 0 alone made the compiler lay the code after it out twice: see gemm_tma.cu).
 __device__ __forceinline__ bool i8_warp_wait(uint64_t* bar, uint32_t parity, int lane) {
-  bool ok = true;
-  if (lane == 0) ok = i8_wait_polite(bar, parity);
-  return __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0;
+  (void)lane;
+  return __all_sync(0xFFFFFFFFu, i8_wait_polite(bar, parity)) != 0;
 }
 // First block whose last byte (stream offset 34 b + 33) lies in box s or later.
 __device__ __forceinline__ int i8_first_block(int s) { return (128 * s) / 34; }
