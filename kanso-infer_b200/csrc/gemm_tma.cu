@@ -20,10 +20,13 @@
 //   * Q4_K: one nibble chunk = 16 low nibbles + 16 high nibbles = two k-steps (sub-blocks 2g
 //     and 2g+1 of the chunk's 64-weight group); header chunks produce nothing and are skipped
 //     by the MMA issuer.
-// 16 producer warps (thread = weight row x chunk) read the raw chunks, dequantise with packed
-// f16 arithmetic (Q8_0: exact int8 -> f16 by byte permute, one rounding in d*q; Q4_K:
+// 16 producer warps (thread = weight row x 32 stream bytes) read the raw chunks, dequantise with
+// packed f16 arithmetic (Q8_0: exact int8 -> f16 by byte permute, one rounding in d*q; Q4_K:
 // d*sc*(q-8) - (dmin*m - 8*d*sc) with both factors rounded once to f16) and store 16-byte
-// core-matrix rows of the A tile (K-major, no swizzle). One warp issues tcgen05.mma
+// core-matrix rows of the A tile (K-major, no swizzle). Where a block's scale or header falls
+// inside a thread's bytes repeats with a short period (17 positions for Q8_0, 9 for Q4_K), so the
+// dequantising code exists once per position, with every selection resolved at compile time, and
+// a switch picks the body. One warp issues tcgen05.mma
 // (kind::f16, M = 128 weight rows, N = up to 256 activation rows per instruction, f32
 // accumulation in up to 512 TMEM columns); one warp streams the packed activations through a
 // ring of bulk copies. All hand-offs are mbarriers with bounded waits: a wait that runs out sets
@@ -48,14 +51,8 @@ constexpr int TM_THREADS = 768;  // 24 warps: scheduler 0 holds the MMA issuer a
 constexpr int TM_TILE_N = 128;                 // weight rows per CTA = MMA M
 constexpr int TM_BOX_W = 128;                  // bytes of a weight row per box (the swizzle span)
 constexpr int TM_BOX = TM_TILE_N * TM_BOX_W;   // 16 KB per ring slot
-#ifndef TM_RAW_SLOTS_N
-#define TM_RAW_SLOTS_N 5
-#endif
-#ifndef TM_A_STAGES_N
-#define TM_A_STAGES_N 2
-#endif
-constexpr int TM_RAW_SLOTS = TM_RAW_SLOTS_N;
-constexpr int TM_A_STAGES = TM_A_STAGES_N;
+constexpr int TM_RAW_SLOTS = 5;  // measured: 4..7 slots and 2 or 3 A stages all within 3 %
+constexpr int TM_A_STAGES = 2;
 constexpr int TM_A_STAGE = 32768;  // 16 k-chunks of 8 positions x 128 rows x 16 bytes
 constexpr int TM_B_SLOTS = 4;
 constexpr int TM_FMT_Q8_0 = 0;
