@@ -47,7 +47,7 @@ extern "C" {
 /* ---- KV pool element type: the reference's KvCacheType flag (src/kv_cache/kind.rs:31-73) ---- */
 #define KANSO_KV_F32 0
 #define KANSO_KV_INT8 1
-#define KANSO_KV_FP8 2 /* parsed, refused with KANSO_ERR_UNSUPPORTED */
+#define KANSO_KV_FP8 2 /* E4M3 bytes, power-of-two scale per (token, kv head) */
 
 typedef struct kanso_cuda_ctx kanso_cuda_ctx;
 typedef struct kanso_cuda_weight kanso_cuda_weight;
@@ -289,10 +289,14 @@ int32_t kanso_cuda_embed(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const 
 
 /* ------------------------------------------------------------------------- */
 /* KV pool: KvStorageKind with the KvCacheType flag — src/kv_cache/kind.rs:176-494,
- * int8 pool src/kv_cache/quantized_storage.rs. */
+ * int8 / fp8 pool src/kv_cache/quantized_storage.rs. */
 
 /* QuantizedKvStorage::new — quantized_storage.rs:56-105. New blocks hold quants 0
- * and scales 1.0 (quantized_storage.rs:24-33). kv_type KANSO_KV_FP8 -> UNSUPPORTED. */
+ * and scales 1.0 (quantized_storage.rs:24-33). kv_type KANSO_KV_INT8 (QuantMode::Int8) or
+ * KANSO_KV_FP8 (QuantMode::Fp8, new_fp8 quantized_storage.rs:109-131: scale =
+ * 2^ceil(log2(amax / 64)), values rounded to nearest-even E4M3, quantized_storage.rs:470-484);
+ * every call that takes the pool (write, read, reset, decode / prefill attention, the decode
+ * step) works on either. KANSO_KV_F32 -> KANSO_ERR_UNSUPPORTED. */
 int32_t kanso_cuda_kv_create(kanso_cuda_ctx* ctx, uint32_t num_layers, uint32_t num_blocks,
                              uint32_t block_size, uint32_t num_kv_heads, uint32_t head_dim,
                              int32_t kv_type, kanso_cuda_kv** out);

@@ -1,5 +1,7 @@
-// int8 KV pool: creation, quantising writes, block reset, token read-back
+// int8 / fp8 KV pool: creation, quantising writes, block reset, token read-back
 // (src/kv_cache/quantized_storage.rs; seam src/kv_cache/kind.rs:176-494).
+#include <cuda_fp8.h>
+
 #include "kv_pool.h"
 
 namespace kanso {
@@ -18,7 +20,7 @@ __global__ void kv_reset_kernel(KvGeom g, uint32_t block_first, uint32_t block_c
   for (uint32_t i = threadIdx.x; i < 2 * g.block_size; i += blockDim.x) s[i] = 1.0f;
 }
 
-// quantize_head_slice, Int8 arm (quantized_storage.rs:452-469) + write_quantized_kv_token
+// quantize_head_slice (quantized_storage.rs:452-484) + write_quantized_kv_token
 // (quantized_storage.rs:143-204). One warp per (token, head, K|V).
 __global__ void kv_write_kernel(KvGeom g, uint32_t layer, const uint32_t* __restrict__ slots,
                                 const float* __restrict__ k, const float* __restrict__ v,
@@ -41,17 +43,36 @@ __global__ void kv_write_kernel(KvGeom g, uint32_t layer, const uint32_t* __rest
   for (uint32_t d = lane; d < g.head_dim; d += 32) amax = fmaxf(amax, fabsf(src[d]));
 #pragma unroll
   for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  float scale = kv_scale_of(amax, g.fp8 != 0);
   float inv = __fdiv_rn(1.0f, scale);
   uint8_t* rec = g.pool + g.rec_offset(layer, block, head);
   int8_t* dst = reinterpret_cast<int8_t*>(rec + (which ? g.v_off() : g.k_off())) +
                 (size_t)off * g.head_dim;
   for (uint32_t d = lane; d < g.head_dim; d += 32) {
-    float r = roundf(__fmul_rn(src[d], inv));
-    dst[d] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
+    const float scaled = __fmul_rn(src[d], inv);
+    if (g.fp8) {
+      // F8E4M3::from_f32: round to nearest even onto the E4M3 grid (quantized_storage.rs:477-482)
+      dst[d] = (int8_t)__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+    } else {
+      dst[d] = (int8_t)fminf(fmaxf(roundf(scaled), -127.f), 127.f);
+    }
   }
   if (lane == 0)
     reinterpret_cast<float*>(rec + (which ? g.vs_off() : g.ks_off()))[off] = scale;
+}
+
+// The value of an E4M3 bit pattern (sign, 4 exponent bits with bias 7, 3 mantissa bits; no
+// infinities, S.1111.111 is NaN): what float8::F8E4M3::to_f32 returns (quantized_storage.rs:440-449).
+static float e4m3_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v;
+  if (e == 15 && m == 7)
+    v = NAN;
+  else if (e == 0)
+    v = ldexpf((float)m, -9);
+  else
+    v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  return (b & 0x80) ? -v : v;
 }
 
 int32_t launch_kv_write(kanso_cuda_ctx* ctx, kanso_cuda_kv* kv, uint32_t layer,
@@ -76,14 +97,11 @@ int32_t kanso_cuda_kv_create(kanso_cuda_ctx* ctx, uint32_t num_layers, uint32_t 
   if (!ctx) return fail(nullptr, KANSO_ERR_CONFIG, "kv_create: ctx is NULL");
   if (!out) return fail(ctx, KANSO_ERR_CONFIG, "kv_create: out is NULL");
   *out = nullptr;
-  if (kv_type == KANSO_KV_FP8)
-    return fail(ctx, KANSO_ERR_UNSUPPORTED,
-                "kv type 'fp8' is not available on backend 'cuda' (expected: int8)");
   if (kv_type == KANSO_KV_F32)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "kv type 'f32' is not available on backend 'cuda': its decode attention reads "
-                "the int8 pool (expected: int8)");
-  if (kv_type != KANSO_KV_INT8)
+                "the quantised pool (expected: int8 or fp8)");
+  if (kv_type != KANSO_KV_INT8 && kv_type != KANSO_KV_FP8)
     return fail(ctx, KANSO_ERR_CONFIG, "unknown kv type %d (expected one of: f32, int8, fp8)",
                 kv_type);
   if (!num_layers || !num_blocks || !block_size || !num_kv_heads || !head_dim)
@@ -192,9 +210,10 @@ int32_t kanso_cuda_kv_read_token(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, u
       size_t i = (size_t)h * kv->head_dim + d;
       if (k_q) k_q[i] = kq[d];
       if (v_q) v_q[i] = vq[d];
-      // (src as f32) * scale, quantized_storage.rs:352-357 — exact on any IEEE host
-      if (k_deq) k_deq[i] = (float)kq[d] * ks;
-      if (v_deq) v_deq[i] = (float)vq[d] * vs;
+      // (src as f32) * scale, or fp8_to_f32(src as u8) * scale (quantized_storage.rs:352-366):
+      // exact on any IEEE host
+      if (k_deq) k_deq[i] = (g.fp8 ? e4m3_to_f32((uint8_t)kq[d]) : (float)kq[d]) * ks;
+      if (v_deq) v_deq[i] = (g.fp8 ? e4m3_to_f32((uint8_t)vq[d]) : (float)vq[d]) * vs;
     }
   }
   return KANSO_OK;

@@ -18,6 +18,8 @@
 // array the merge runs inside stage 1, in the CTA that finishes last for its (sequence, kv head):
 // every CTA publishes its partials, fences, and takes a ticket; the one that draws the last
 // ticket reads all partials back. Nothing waits on anything, so there is no spin to bound.
+#include <cuda_fp8.h>
+
 #include <mutex>
 #include <vector>
 
@@ -101,8 +103,21 @@ __device__ __forceinline__ uint32_t pa_clamp_ctx(const PaArgs& a, uint32_t ctx, 
   return ctx;
 }
 
-// NT = threads per CTA.
-template <int G, int NT>
+// Eight E4M3 values (two words) -> f32, exactly (every E4M3 number is an f16 number).
+__device__ __forceinline__ void e4m3x4_to_f32(uint32_t w, float* f) {
+  const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xFFFFu), __NV_E4M3);
+  const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
+  const float2 a = __half22float2(__half2(lo)), b = __half22float2(__half2(hi));
+  f[0] = a.x;
+  f[1] = a.y;
+  f[2] = b.x;
+  f[3] = b.y;
+}
+
+// NT = threads per CTA. FP8: the pool holds E4M3 bit patterns with power-of-two scales
+// (src/kv_cache/quantized_storage.rs:470-484); the query then stays in f32 and the products are
+// f32 multiply-adds on the exactly converted K and V values. Otherwise int8 with dp4a.
+template <int G, int NT, bool FP8>
 __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
@@ -141,7 +156,8 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   uint64_t* bar = reinterpret_cast<uint64_t*>(tiles + (size_t)max_blk * a.g.rec_bytes);
   int8_t* qhi = reinterpret_cast<int8_t*>(bar + 2);          // [G][hd]
   int8_t* qlo = qhi + G * hd;                                // [G][hd]
-  float* qd = reinterpret_cast<float*>(qlo + G * hd);        // [G] (d/254)
+  float* qf = reinterpret_cast<float*>(qhi);                 // FP8: [G][hd] f32 instead of the planes
+  float* qd = reinterpret_cast<float*>(qhi + (FP8 ? 4 : 2) * G * hd);  // [G] (d/254)
   uint32_t* blk = reinterpret_cast<uint32_t*>(qd + PA_MAX_GROUP);  // [part_tokens/bs + 1]
   const uint32_t nblk_part = (max_blk + 4) & ~3u;
   float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
@@ -227,7 +243,7 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    new_scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    new_scale = kv_scale_of(amax, FP8);
     new_inv = __fdiv_rn(1.0f, new_scale);
   }
   for (int gq = warp; gq < G; gq += NT / 32) {
@@ -242,6 +258,14 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (FP8) {
+#pragma unroll
+      for (int i = 0; i < QE; ++i) {
+        const uint32_t d = lane + 32 * i;
+        if (d < hd) qf[gq * hd + d] = qe[i];
+      }
+      continue;
+    }
     float d_ = amax / 127.0f;
     float id = d_ != 0.f ? 1.0f / d_ : 0.f;
 #pragma unroll
@@ -275,7 +299,10 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
       for (int i = 0; i < QE; ++i) {
         const uint32_t d = lane + 32 * i;
         if (d < hd) {
-          const int8_t qv = (int8_t)fminf(fmaxf(roundf(__fmul_rn(ne[i], new_inv)), -127.f), 127.f);
+          const float scaled = __fmul_rn(ne[i], new_inv);
+          const int8_t qv =
+              FP8 ? (int8_t)__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3)
+                  : (int8_t)fminf(fmaxf(roundf(scaled), -127.f), 127.f);
           dst[d] = qv;
           mine[d] = qv;
         }
@@ -302,6 +329,39 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     const uint32_t off = qk_it.off;
     const uint4* krow = reinterpret_cast<const uint4*>(rec + a.g.k_off() + (size_t)off * hd);
     const float ksc = reinterpret_cast<const float*>(rec + a.g.ks_off())[off];
+    if (FP8) {
+      float dot[G];
+#pragma unroll
+      for (int gq = 0; gq < G; ++gq) dot[gq] = 0.f;
+      for (uint32_t cc = 0; cc < nchunk; ++cc) {
+        const uint32_t c = (cc + (i >> 1)) & (nchunk - 1);
+        const uint4 kw = krow[c];
+        float kf[16];
+        e4m3x4_to_f32(kw.x, kf);
+        e4m3x4_to_f32(kw.y, kf + 4);
+        e4m3x4_to_f32(kw.z, kf + 8);
+        e4m3x4_to_f32(kw.w, kf + 12);
+#pragma unroll
+        for (int gq = 0; gq < G; ++gq) {
+          const float4* q4 = reinterpret_cast<const float4*>(qf + gq * hd + 16 * c);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 qq = q4[j];
+            dot[gq] = fmaf(kf[4 * j], qq.x, dot[gq]);
+            dot[gq] = fmaf(kf[4 * j + 1], qq.y, dot[gq]);
+            dot[gq] = fmaf(kf[4 * j + 2], qq.z, dot[gq]);
+            dot[gq] = fmaf(kf[4 * j + 3], qq.w, dot[gq]);
+          }
+        }
+      }
+#pragma unroll
+      for (int gq = 0; gq < G; ++gq) {
+        const float sc = dot[gq] * ksc * a.scale;
+        prob[gq * a.part_tokens + i] = sc;
+        lmax[gq] = fmaxf(lmax[gq], sc);
+      }
+      continue;
+    }
     int ih[G], il[G];
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) ih[gq] = il[gq] = 0;
@@ -389,12 +449,17 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     const uint8_t* rec = tiles + (size_t)pv_it.blk * a.g.rec_bytes;
     const uint2 vw =
         reinterpret_cast<const uint2*>(rec + a.g.v_off() + (size_t)pv_it.off * hd)[c];
-    const uint32_t lo = vw.x ^ 0x80808080u, hi = vw.y ^ 0x80808080u;
     float f[8];
+    if (FP8) {
+      e4m3x4_to_f32(vw.x, f);
+      e4m3x4_to_f32(vw.y, f + 4);
+    } else {
+      const uint32_t lo = vw.x ^ 0x80808080u, hi = vw.y ^ 0x80808080u;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      f[k] = s8_to_f32(lo, k);
-      f[4 + k] = s8_to_f32(hi, k);
+      for (int k = 0; k < 4; ++k) {
+        f[k] = s8_to_f32(lo, k);
+        f[4 + k] = s8_to_f32(hi, k);
+      }
     }
 #pragma unroll
     for (int gq = 0; gq < G; ++gq) {
@@ -553,35 +618,44 @@ static int32_t validate_params(const kanso_paged_attention_params* p, char* msg,
 // Dynamic shared memory of stage 1: the partition's block records, query planes and scales,
 // block ids, probabilities, PV reduction scratch.
 static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t block_size,
-                             uint32_t rec_bytes, uint32_t threads) {
+                             uint32_t rec_bytes, uint32_t threads, bool fp8 = false) {
   const uint32_t max_blk = (pt + block_size - 1) / block_size;
   const uint32_t nblk_part = (max_blk + 4) & ~3u;
   const uint32_t dwords = hd / 8, nslice = threads / dwords;
-  size_t smem = (size_t)max_blk * rec_bytes + 16 + 2 * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 +
+  size_t smem = (size_t)max_blk * rec_bytes + 16 + (fp8 ? 4 : 2) * G * hd + PA_MAX_GROUP * 4 +
+                nblk_part * 4 +
                 (size_t)((G * pt + 3) & ~3u) * 4;
   size_t red_bytes = (size_t)nslice * G * hd * 4;
   if (red_bytes < 128) red_bytes = 128;
   return smem + red_bytes;
 }
 
-template <int G, int NT>
+template <int G, int NT, bool FP8>
 static void launch_stage1_nt(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
   static size_t smem_set[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (smem > smem_set[dev & 15]) {
-    cudaFuncSetAttribute(paged_attn_stage1<G, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)smem);
+    cudaFuncSetAttribute(paged_attn_stage1<G, NT, FP8>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     smem_set[dev & 15] = smem;
   }
-  launch_dependent(ctx, paged_attn_stage1<G, NT>, grid, dim3(NT), smem, a);
+  launch_dependent(ctx, paged_attn_stage1<G, NT, FP8>, grid, dim3(NT), smem, a);
 }
 template <int G>
 static void launch_stage1(kanso_cuda_ctx* ctx, const PaArgs& a, dim3 grid, size_t smem) {
-  if (pa_threads(a.part_tokens) == PA_BIG_THREADS)
-    launch_stage1_nt<G, PA_BIG_THREADS>(ctx, a, grid, smem);
-  else
-    launch_stage1_nt<G, PA_THREADS>(ctx, a, grid, smem);
+  const bool big = pa_threads(a.part_tokens) == PA_BIG_THREADS;
+  if (a.g.fp8) {
+    if (big)
+      launch_stage1_nt<G, PA_BIG_THREADS, true>(ctx, a, grid, smem);
+    else
+      launch_stage1_nt<G, PA_THREADS, true>(ctx, a, grid, smem);
+  } else {
+    if (big)
+      launch_stage1_nt<G, PA_BIG_THREADS, false>(ctx, a, grid, smem);
+    else
+      launch_stage1_nt<G, PA_THREADS, false>(ctx, a, grid, smem);
+  }
 }
 
 int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uint32_t layer,
@@ -617,7 +691,7 @@ int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv
     pt >>= 1;
   // the partition's records are staged in shared memory: two CTAs per SM when possible
   while (pt > 64 &&
-         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt)) > (size_t)ctx->smem_optin / 2)
+         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0) > (size_t)ctx->smem_optin / 2)
     pt >>= 1;
   // whole blocks per partition: a partition starts on a block record
   if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
@@ -662,7 +736,7 @@ int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv
     a.table_len = fusion->table_len;
   }
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt));
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED, "paged attention: %zu bytes of shared memory needed",
                 smem);
@@ -873,7 +947,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
                         (uint64_t)ctx->sm_count / 2)
     pt >>= 1;
   while (pt > 64 &&
-         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt)) > (size_t)ctx->smem_optin / 2)
+         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0) > (size_t)ctx->smem_optin / 2)
     pt >>= 1;
   if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
@@ -916,7 +990,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.positions = a.slots = nullptr;
   a.table_len = 0;
 
-  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt));
+  const size_t smem = pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0);
   if (smem > (size_t)ctx->smem_optin)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "paged_attention_noalloc: %zu bytes of shared memory needed", smem);

@@ -7,6 +7,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <limits>
 #include <vector>
 
 namespace {
@@ -398,7 +399,7 @@ void kanso_ref_quantize_weights_q4_k(const float* w, int64_t rows, int64_t cols,
   }
 }
 
-/* ------------------------------ int8 KV pool ------------------------------ */
+/* --------------------------- int8 / fp8 KV pool --------------------------- */
 
 struct kanso_ref_kv {
   uint32_t layers, num_blocks, block_size, kv_heads, head_dim;
@@ -406,6 +407,7 @@ struct kanso_ref_kv {
   // scales [offset][head] (src/kv_cache/quantized_storage.rs:16-21).
   std::vector<int8_t> kq, vq;
   std::vector<float> ks, vs;
+  int32_t fp8 = 0;  // QuantMode::Fp8: the bytes are E4M3 bit patterns (quantized_storage.rs:7-10)
   size_t q_per_block() const { return (size_t)block_size * kv_heads * head_dim; }
   size_t s_per_block() const { return (size_t)block_size * kv_heads; }
   size_t blk(uint32_t layer, uint32_t block) const { return (size_t)layer * num_blocks + block; }
@@ -421,6 +423,71 @@ float kanso_ref_kv_quantize_head(const float* x, int32_t n, int8_t* q) {
   float inv = 1.0f / scale;
   for (int i = 0; i < n; ++i) q[i] = round_clamp_i8(x[i] * inv, -127.0f, 127.0f);
   return scale;
+}
+
+/* float8::F8E4M3 (crate float8 0.7.0, not vendored in the reference tree): the OCP E4M3 format,
+ * 1 sign, 4 exponent bits with bias 7, 3 mantissa bits, no infinities, S.1111.111 = NaN, largest
+ * finite value 448. Restated from the published format; conversion from f32 rounds to nearest,
+ * ties to even, subnormals (multiples of 2^-9) included. The quantiser below never produces a
+ * magnitude above 64, so the overflow rule of the crate is not exercised. */
+float kanso_ref_fp8_e4m3_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v;
+  if (e == 15 && m == 7)
+    v = std::numeric_limits<float>::quiet_NaN();
+  else if (e == 0)
+    v = std::ldexp((float)m, -9);
+  else
+    v = std::ldexp(1.0f + (float)m / 8.0f, e - 7);
+  return (b & 0x80) ? -v : v;
+}
+
+uint8_t kanso_ref_fp8_e4m3_from_f32(float x) {
+  const uint8_t sign = std::signbit(x) ? 0x80 : 0;
+  if (std::isnan(x)) return sign | 0x7F;
+  const float a = std::fabs(x);
+  if (a >= 464.0f) return sign | 0x7E;  // beyond the midpoint above 448: saturate
+  if (a < 0.015625f) {                   // below 2^-6: subnormal grid of 2^-9
+    const int q = (int)std::nearbyint(std::ldexp(a, 9));  // ties to even; 8 becomes the first normal
+    return sign | (uint8_t)q;
+  }
+  int e;
+  std::frexp(a, &e);  // a = m * 2^e, m in [0.5, 1): exponent of the leading bit is e - 1
+  int ex = e - 1;
+  int q = (int)std::nearbyint(std::ldexp(a, 3 - ex));  // 8..16
+  if (q == 16) {
+    q = 8;
+    ++ex;
+  }
+  if (ex > 8) return sign | 0x7E;
+  uint8_t bits = (uint8_t)(((ex + 7) << 3) | (q - 8));
+  if (bits == 0x7F) bits = 0x7E;
+  return sign | bits;
+}
+
+/* quantize_head_slice, Fp8 arm (quantized_storage.rs:470-484), written as the reference writes
+ * it: scale = 2^ceil(log2(amax / 64)) through the platform's f32 log2. */
+float kanso_ref_kv_quantize_head_fp8(const float* x, int32_t n, int8_t* q) {
+  float amax = 0.0f;
+  for (int i = 0; i < n; ++i) {
+    float ax = std::fabs(x[i]);
+    if (ax > amax) amax = ax;
+  }
+  float scale = 1.0f;
+  if (amax > 0.0f) {
+    const int exp = (int)std::ceil(std::log2(amax / 64.0f));
+    scale = std::ldexp(1.0f, exp);  // 2.0f32.powi(exp)
+  }
+  const float inv = 1.0f / scale;
+  for (int i = 0; i < n; ++i) q[i] = (int8_t)kanso_ref_fp8_e4m3_from_f32(x[i] * inv);
+  return scale;
+}
+
+kanso_ref_kv* kanso_ref_kv_create_typed(uint32_t layers, uint32_t num_blocks, uint32_t block_size,
+                                        uint32_t kv_heads, uint32_t head_dim, int32_t fp8) {
+  kanso_ref_kv* kv = kanso_ref_kv_create(layers, num_blocks, block_size, kv_heads, head_dim);
+  kv->fp8 = fp8 ? 1 : 0;
+  return kv;
 }
 
 kanso_ref_kv* kanso_ref_kv_create(uint32_t layers, uint32_t num_blocks, uint32_t block_size,
@@ -446,8 +513,13 @@ int32_t kanso_ref_kv_write_token(kanso_ref_kv* kv, uint32_t layer, uint32_t bloc
   for (uint32_t h = 0; h < H; ++h) {
     size_t si = b * kv->s_per_block() + (size_t)offset * H + h;
     size_t qi = b * kv->q_per_block() + (size_t)offset * H * hd + (size_t)h * hd;
-    kv->ks[si] = kanso_ref_kv_quantize_head(k + h * hd, (int32_t)hd, &kv->kq[qi]);
-    kv->vs[si] = kanso_ref_kv_quantize_head(v + h * hd, (int32_t)hd, &kv->vq[qi]);
+    if (kv->fp8) {
+      kv->ks[si] = kanso_ref_kv_quantize_head_fp8(k + h * hd, (int32_t)hd, &kv->kq[qi]);
+      kv->vs[si] = kanso_ref_kv_quantize_head_fp8(v + h * hd, (int32_t)hd, &kv->vq[qi]);
+    } else {
+      kv->ks[si] = kanso_ref_kv_quantize_head(k + h * hd, (int32_t)hd, &kv->kq[qi]);
+      kv->vs[si] = kanso_ref_kv_quantize_head(v + h * hd, (int32_t)hd, &kv->vq[qi]);
+    }
   }
   return ST_OK;
 }
@@ -476,6 +548,11 @@ void kanso_ref_kv_reset_block(kanso_ref_kv* kv, uint32_t block) {
   }
 }
 
+/* (src as f32), or fp8_to_f32(src as u8) (quantized_storage.rs:352-366) */
+static inline float kv_value(const kanso_ref_kv* kv, int8_t b) {
+  return kv->fp8 ? kanso_ref_fp8_e4m3_to_f32((uint8_t)b) : (float)b;
+}
+
 int32_t kanso_ref_kv_read_token(const kanso_ref_kv* kv, uint32_t layer, uint32_t block,
                                 uint32_t offset, int8_t* k_q, int8_t* v_q, float* k_scale,
                                 float* v_scale, float* k_deq, float* v_deq) {
@@ -491,8 +568,8 @@ int32_t kanso_ref_kv_read_token(const kanso_ref_kv* kv, uint32_t layer, uint32_t
     for (uint32_t d = 0; d < hd; ++d) {
       if (k_q) k_q[h * hd + d] = kv->kq[qi + d];
       if (v_q) v_q[h * hd + d] = kv->vq[qi + d];
-      if (k_deq) k_deq[h * hd + d] = (float)kv->kq[qi + d] * kv->ks[si];
-      if (v_deq) v_deq[h * hd + d] = (float)kv->vq[qi + d] * kv->vs[si];
+      if (k_deq) k_deq[h * hd + d] = kv_value(kv, kv->kq[qi + d]) * kv->ks[si];
+      if (v_deq) v_deq[h * hd + d] = kv_value(kv, kv->vq[qi + d]) * kv->vs[si];
     }
   }
   return ST_OK;
@@ -514,8 +591,8 @@ int32_t kanso_ref_kv_gather(const kanso_ref_kv* kv, uint32_t layer, const uint32
       float* kd = k_out + ((size_t)t * H + h) * hd;
       float* vd = v_out + ((size_t)t * H + h) * hd;
       for (uint32_t d = 0; d < hd; ++d) {
-        kd[d] = (float)kv->kq[qi + d] * ksc;
-        vd[d] = (float)kv->vq[qi + d] * vsc;
+        kd[d] = kv_value(kv, kv->kq[qi + d]) * ksc;
+        vd[d] = kv_value(kv, kv->vq[qi + d]) * vsc;
       }
     }
   }

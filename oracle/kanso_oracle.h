@@ -84,12 +84,20 @@ void kanso_ref_gemm_q4_k(const uint8_t* w, const float* x, float* y, int64_t M, 
 void kanso_ref_quantize_weights_q4_k(const float* w, int64_t rows, int64_t cols,
                                      uint8_t* gguf_out);
 
-/* ---- int8 KV pool: src/kv_cache/quantized_storage.rs ---- */
+/* ---- int8 / fp8 KV pool: src/kv_cache/quantized_storage.rs ---- */
 typedef struct kanso_ref_kv kanso_ref_kv;
 /* quantize_head_slice, Int8 arm (quantized_storage.rs:452-469). Returns the scale. */
 float kanso_ref_kv_quantize_head(const float* x, int32_t n, int8_t* q);
 kanso_ref_kv* kanso_ref_kv_create(uint32_t layers, uint32_t num_blocks, uint32_t block_size,
                                   uint32_t kv_heads, uint32_t head_dim);
+/* The same pool in QuantMode::Fp8 when fp8 != 0 (QuantizedKvStorage::new_fp8,
+ * quantized_storage.rs:109-131). */
+kanso_ref_kv* kanso_ref_kv_create_typed(uint32_t layers, uint32_t num_blocks, uint32_t block_size,
+                                        uint32_t kv_heads, uint32_t head_dim, int32_t fp8);
+/* quantize_head_slice, Fp8 arm (quantized_storage.rs:470-484); E4M3 per the float8 crate. */
+float kanso_ref_kv_quantize_head_fp8(const float* x, int32_t n, int8_t* q);
+float kanso_ref_fp8_e4m3_to_f32(uint8_t bits);
+uint8_t kanso_ref_fp8_e4m3_from_f32(float x);
 void kanso_ref_kv_destroy(kanso_ref_kv* kv);
 /* write_quantized_kv_token (quantized_storage.rs:143-204); status as the C ABI's. */
 int32_t kanso_ref_kv_write_token(kanso_ref_kv* kv, uint32_t layer, uint32_t block,

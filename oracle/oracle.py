@@ -88,6 +88,13 @@ def lib():
         L.kanso_ref_kv_quantize_head.restype = C.c_float
         L.kanso_ref_kv_create.restype = C.c_void_p
         L.kanso_ref_kv_create.argtypes = [C.c_uint32] * 5
+        L.kanso_ref_kv_create_typed.restype = C.c_void_p
+        L.kanso_ref_kv_create_typed.argtypes = [C.c_uint32] * 5 + [C.c_int32]
+        L.kanso_ref_kv_quantize_head_fp8.restype = C.c_float
+        L.kanso_ref_fp8_e4m3_to_f32.restype = C.c_float
+        L.kanso_ref_fp8_e4m3_to_f32.argtypes = [C.c_uint8]
+        L.kanso_ref_fp8_e4m3_from_f32.restype = C.c_uint8
+        L.kanso_ref_fp8_e4m3_from_f32.argtypes = [C.c_float]
         L.kanso_ref_kv_destroy.argtypes = [C.c_void_p]
         L.kanso_ref_model_create.restype = C.c_void_p
         L.kanso_ref_model_destroy.argtypes = [C.c_void_p]
@@ -251,11 +258,27 @@ def kv_quantize_head(x):
     return np.float32(s), q
 
 
+def kv_quantize_head_fp8(x):
+    x = _f32(x)
+    q = np.empty(x.size, np.int8)
+    s = lib().kanso_ref_kv_quantize_head_fp8(_p(x), C.c_int32(x.size), _p(q))
+    return np.float32(s), q
+
+
+def fp8_e4m3_to_f32(bits):
+    return np.float32(lib().kanso_ref_fp8_e4m3_to_f32(C.c_uint8(int(bits) & 0xFF)))
+
+
+def fp8_e4m3_from_f32(x):
+    return int(lib().kanso_ref_fp8_e4m3_from_f32(C.c_float(float(x))))
+
+
 class KvPool:
-    def __init__(self, layers, num_blocks, block_size, kv_heads, head_dim):
+    def __init__(self, layers, num_blocks, block_size, kv_heads, head_dim, fp8=False):
         self.geom = (layers, num_blocks, block_size, kv_heads, head_dim)
-        self.h = C.c_void_p(lib().kanso_ref_kv_create(layers, num_blocks, block_size, kv_heads,
-                                                      head_dim))
+        self.fp8 = bool(fp8)
+        self.h = C.c_void_p(lib().kanso_ref_kv_create_typed(layers, num_blocks, block_size,
+                                                            kv_heads, head_dim, int(self.fp8)))
 
     def __del__(self):
         if getattr(self, "h", None):

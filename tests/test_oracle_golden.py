@@ -1,5 +1,6 @@
 """CPU: the oracle against the committed golden fixtures and the reference's own test bounds."""
 import numpy as np
+import pytest
 
 from conftest import golden, rel_err
 
@@ -91,6 +92,50 @@ def test_kv_int8(oracle):
     # a recycled block in another layer is erased too
     st, got0 = pool.read_token(0, 2, 0)
     assert np.all(got0["v_scale"] == 1.0)
+
+
+def test_kv_fp8(oracle):
+    """QuantMode::Fp8 (src/kv_cache/quantized_storage.rs:109-131,440-449,470-484). E4M3 itself
+    comes from the float8 crate, which the reference tree does not vendor: the restatement is
+    pinned on the format's fixed points, on the reference's own test vector
+    (tests/test_quantized_kv_cache.rs:88-166) and on an independent implementation (torch's
+    float8_e4m3fn conversion) over seeded values of every binade, subnormals included."""
+    torch = pytest.importorskip("torch")
+    val = [oracle.fp8_e4m3_to_f32(b) for b in range(256)]
+    assert val[0x7E] == 448.0 and val[0x08] == 2.0 ** -6 and val[0x01] == 2.0 ** -9
+    assert val[0x38] == 1.0 and val[0xB8] == -1.0 and val[0x7F] != val[0x7F]
+    for b in range(256):
+        if val[b] == val[b] and val[b] != 0:
+            assert oracle.fp8_e4m3_from_f32(val[b]) == b
+    assert oracle.fp8_e4m3_from_f32(1.0625) == 0x38 and oracle.fp8_e4m3_from_f32(1.1875) == 0x3A
+    rng = np.random.Generator(np.random.PCG64(0xB200F8))
+    x = (rng.standard_normal(20000) * 10.0 ** rng.uniform(-4, 2, 20000)).astype(np.float32)
+    x = x[np.abs(x) <= 448]
+    ref = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = np.array([oracle.fp8_e4m3_from_f32(v) for v in x], np.uint8)
+    assert np.array_equal(got, ref)
+    back = torch.from_numpy(np.arange(256, dtype=np.uint8)).view(torch.float8_e4m3fn).float().numpy()
+    assert all(back[b] == val[b] for b in range(256) if val[b] == val[b])
+    # the reference's own case: values E4M3 holds exactly, bound 1 %, here zero
+    n = 4 * 64
+    k = np.array([((i % 16) * 0.5 - 3.5) or 1.0 for i in range(n)], np.float32)
+    v = np.array([(i % 8) + 0.5 for i in range(n)], np.float32)
+    pool = oracle.KvPool(2, 4, 4, 4, 64, fp8=True)
+    assert pool.write_token(0, 0, 0, k, v) == 0
+    st, got = pool.read_token(0, 0, 0)
+    assert st == 0 and np.array_equal(got["k_deq"], k) and np.array_equal(got["v_deq"], v)
+    assert np.all(got["k_scale"] == np.float32(2.0 ** -4)) and np.all(got["v_scale"] == 0.125)
+    # seeded rows: scale is the smallest power of two >= amax / 64, error within half an E4M3 step
+    xs = rng.standard_normal((16, 64)).astype(np.float32) * 3
+    for row in xs:
+        sc, q = oracle.kv_quantize_head_fp8(row)
+        amax = float(np.max(np.abs(row)))
+        assert sc >= amax / 64 > sc / 2 and np.log2(sc) == round(np.log2(sc))
+        deq = np.array([oracle.fp8_e4m3_to_f32(int(b) & 0xFF) for b in q], np.float32) * sc
+        assert np.all(np.abs(deq - row) <= np.maximum(np.abs(row) / 16, sc * 2.0 ** -10))
+    # same byte count per token as int8 (quantized_storage.rs:414-419); fresh blocks: 0 / 1.0
+    st, fresh = pool.read_token(1, 3, 1)
+    assert not fresh["k_q"].any() and np.all(fresh["v_scale"] == 1.0)
 
 
 def test_paged_attention_kat(oracle):
