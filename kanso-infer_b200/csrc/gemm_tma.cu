@@ -686,7 +686,7 @@ int32_t tma_encode_weight_map(const void* w, int64_t row_bytes, int64_t N, CUten
   return cr == CUDA_SUCCESS ? KANSO_OK : KANSO_ERR_DEVICE;
 }
 
-// y[M,N] = x[M,K] @ W^T for 9..512 activation rows. Sets *handled = false (and launches
+// y[M,N] = x[M,K] @ W^T for 9..512 activation rows (Q8_0: 2..512). Sets *handled = false (and launches
 // nothing) when the shape is outside this kernel's range: rows of the block matrix must start
 // on 16-byte boundaries (every Q4_K matrix; Q8_0 when K % 256 == 0).
 int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x, float* y,
@@ -695,7 +695,9 @@ int32_t tma_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const floa
   if (dtype != KANSO_DTYPE_Q8_0 && dtype != KANSO_DTYPE_Q4_K) return KANSO_OK;
   const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
   const int bb = dtype == KANSO_DTYPE_Q8_0 ? Q8_BYTES : Q4K_BYTES;
-  if (M < 9 || M > TM_MAX_M || N < 1 || K < blk || K % blk != 0 || !w || !x || !y) return KANSO_OK;
+  const int64_t min_m = dtype == KANSO_DTYPE_Q8_0 ? 2 : 9;  // below: the GEMV kernels are faster
+  if (M < min_m || M > TM_MAX_M || N < 1 || K < blk || K % blk != 0 || !w || !x || !y)
+    return KANSO_OK;
   const int64_t row_bytes = K / blk * bb;
   if (row_bytes % 16 != 0 || !aligned16(w) || row_bytes > (1 << 28) || N > (1 << 30))
     return KANSO_OK;

@@ -24,8 +24,12 @@ int32_t i8_matmul(kanso_cuda_ctx* ctx, const void* w, const float* x, float* y, 
 int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float* x,
                         float* y, int64_t M, int64_t N, int64_t K, int32_t act_mode) {
   // More than 8 activation rows on a matrix whose rows start on 16-byte boundaries: the
-  // TMA-staged tcgen05 GEMM, up to 512 rows per pass over the weights.
-  if (M > 8 && act_mode == KANSO_ACT_F32 && N > 0 && K > 0 && w && x && y) {
+  // TMA-staged tcgen05 GEMM, up to 512 rows per pass over the weights. Q8_0 takes it from two
+  // rows on: measured on 14336 x 4096 / 4096 x 4096 / 4096 x 14336 it needs 31.8 / 11.9 / 30.0 us
+  // at up to 16 rows, the int8-MMA GEMV 30.8 / 14.1 / 40.6 us at two rows and 37.5 / 15.3 /
+  // 50.4 us at eight (one row stays with the GEMV: 23.8 / 10.0 / 26.4 us).
+  const bool tma_rows = M > 8 || (M >= 2 && dtype == KANSO_DTYPE_Q8_0);
+  if (tma_rows && act_mode == KANSO_ACT_F32 && N > 0 && K > 0 && w && x && y) {
     bool all = true;
     for (int64_t m0 = 0; m0 < M && all; m0 += 512) {
       bool handled = false;
