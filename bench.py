@@ -757,7 +757,7 @@ def run_sharded(args, torch, dist, kb, O, ctx, stream, rank, world, local):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    us_per_gemv = us_step / (2 * pairs)  # the wait-and-sum kernel's time is charged to the GEMVs
+    us_per_gemv = us_step / (2 * pairs)  # exchange and sum run inside the down GEMV's last CTA
     per_launch_bytes = (alg_bytes(*UP) + alg_bytes(*DOWN)) / 2
     achieved = per_launch_bytes / us_per_gemv / 1e3
     line = {
@@ -773,15 +773,16 @@ def run_sharded(args, torch, dist, kb, O, ctx, stream, rank, world, local):
             "ring_pairs": pairs, "bytes_per_step_per_gpu": step_bytes,
             "l2": f"inputs larger than L2: {step_bytes / 1e6:.0f} MB of distinct weights per "
                   "GPU per step vs 126 MB L2",
-            "launch": "CUDA graph of the step (3 kernels per pair: up GEMV, down GEMV storing to "
-                      "every rank and signalling, wait-and-sum)",
+            "launch": "CUDA graph of the step (2 kernels per pair: up GEMV; down GEMV whose last "
+                      "CTA stores its partial sums to every rank, signals, waits for the peers "
+                      "and adds)",
             "parallelism": f"row shard -> K shard over {world} GPUs, no NCCL call on the data path",
             "check_vs_oracle": check},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
-                     "kernel": "gemv_q4k_mma_kernel (+ shard_wait_sum_kernel per pair)",
+                     "kernel": "gemv_q4k_mma_kernel (exchange fused into its last CTA)",
                      "us_per_launch": us_per_gemv, "alg_bytes_per_launch": per_launch_bytes},
-        "e2e": e2e, "gpu_launches": 3 * pairs * args.steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": 2 * pairs * args.steps, "clocks": clocks,
     }
     if cfg5:
         line["cfg5_sharded"] = cfg5
