@@ -73,7 +73,7 @@ int32_t matmul_dispatch(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const
     }
     if (all) return KANSO_OK;
   }
-  if (dtype == KANSO_DTYPE_Q4_K && act_mode == KANSO_ACT_F32 && K > 0 && K % 2048 == 0 && M > 0 &&
+  if (dtype == KANSO_DTYPE_Q4_K && act_mode == KANSO_ACT_F32 && K > 0 && K % 256 == 0 && M > 0 &&
       N > 0 && w && x && y && aligned16(w) && aligned16(x)) {
     // int8 tensor-core GEMV. Up to 6 activation rows go in one pass over the weights; from 7
     // rows on, passes of 4 are faster than the kernel's 7- and 8-row forms (which spill

@@ -62,15 +62,16 @@ __device__ __forceinline__ void shard_ticket(const ShardSignal& s, unsigned int 
 __device__ __forceinline__ void shard_wait_flags(const unsigned long long* mine, int world,
                                                  unsigned long long e, int* status) {
   if ((int)threadIdx.x < world) {
-    unsigned long long t0, t1, seen;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    unsigned long long t0 = 0, t1, seen;
     for (;;) {
       asm volatile("ld.acquire.sys.global.u64 %0, [%1];"
                    : "=l"(seen)
                    : "l"(mine + threadIdx.x)
                    : "memory");
       if (seen >= e) break;
+      // the clock is only read once the flag was found unset (a read costs about 150 ns)
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t0 == 0) t0 = t1;
       if (t1 - t0 > 2000000000ull) {  // 2 s
         atomicOr(status, (int)DEV_WAIT_TIMEOUT);
         break;
@@ -91,30 +92,67 @@ __device__ __forceinline__ void shard_tail(const ShardSignal& s) {
   if (!s.signal) return;  // an earlier pass: its rows are published by the last pass
   const unsigned long long e = *s.step + 1;
   const int64_t par = (int64_t)((e - 1) & 1ull) * s.buf_stride;
-  const int64_t total = (int64_t)s.m_total * s.n;
-  for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
-    const int64_t m = i / s.n, c = i - m * s.n;
-    const float v = __ldcg(s.stage + i);
-    for (int r = 0; r < s.world; ++r) s.out[r][par + m * s.ld + s.col0 + c] = v;
+  const int n = (int)s.n, world = s.world, rank = s.rank;
+  // 16-byte moves when every row of the slice starts on a 16-byte boundary in both places
+  // (stage rows are n floats apart, buffer rows ld floats, the slice starts at col0)
+  const bool vec = ((n | (int)s.col0 | (int)s.ld) & 3) == 0;
+  // The slice goes to every PEER's buffer; this rank reads its own part from the stage.
+  for (int m = 0; m < s.m_total; ++m) {
+    const float* src = s.stage + (int64_t)m * n;
+    const int64_t dst = par + (int64_t)m * s.ld + s.col0;
+    if (vec) {
+      for (int c = 4 * (int)threadIdx.x; c < n; c += 4 * (int)blockDim.x) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + c));
+        for (int r = 0; r < world; ++r)
+          if (r != rank || !s.sum) *reinterpret_cast<float4*>(s.out[r] + dst + c) = v;
+      }
+    } else {
+      for (int c = (int)threadIdx.x; c < n; c += (int)blockDim.x) {
+        const float v = __ldcg(src + c);
+        for (int r = 0; r < world; ++r)
+          if (r != rank || !s.sum) s.out[r][dst + c] = v;
+      }
+    }
   }
   // one system-scope fence per storing thread, then thread r tells rank r (one store each, in
   // parallel: a release store per peer from one thread would pay a fence per peer)
   __threadfence_system();
   __syncthreads();
-  if ((int)threadIdx.x < s.world)
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s.flags[threadIdx.x] + s.rank),
+  if ((int)threadIdx.x < world)
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s.flags[threadIdx.x] + rank),
                  "l"(e)
                  : "memory");
   if (threadIdx.x == 0) *s.step = e;
   if (!s.sum) return;
-  shard_wait_flags(s.flags[s.rank], s.world, e, s.status);
-  const float* buf = s.out[s.rank] + par;  // this rank's own copy of the exchange buffer
-  for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
-    const int64_t m = i / s.n, c = i - m * s.n;
-    const float* p = buf + m * s.ld + c;
-    float acc = 0.f;
-    for (int r = 0; r < s.world; ++r) acc += __ldcg(p + (int64_t)r * s.n);
-    s.y[i] = acc;
+  shard_wait_flags(s.flags[rank], world, e, s.status);
+  // K shard: the buffer holds `world` slices of n floats per row (slice r from rank r, col0 =
+  // rank * n); add them in rank order, this rank's own from the stage
+  const float* buf = s.out[rank] + par;
+  for (int m = 0; m < s.m_total; ++m) {
+    const float* mine = s.stage + (int64_t)m * n;
+    const float* row = buf + (int64_t)m * s.ld;
+    float* y = s.y + (int64_t)m * n;
+    if (vec) {
+      for (int c = 4 * (int)threadIdx.x; c < n; c += 4 * (int)blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(
+              r == rank ? mine + c : row + (int64_t)r * n + c));
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(y + c) = acc;
+      }
+    } else {
+      for (int c = (int)threadIdx.x; c < n; c += (int)blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < world; ++r)
+          acc += __ldcg(r == rank ? mine + c : row + (int64_t)r * n + c);
+        y[c] = acc;
+      }
+    }
   }
 }
 
