@@ -103,14 +103,32 @@ int32_t kanso_cuda_linear(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, const
 // four driver calls and their gaps on the stream become one, which is most of what a host
 // call costs around a 10 us kernel. A capture that cannot be made (the caller is itself
 // capturing this stream, or the driver refuses) leaves the plain sequence in place.
+// The device status word -> the pinned host word the caller watches. It runs after the matmul
+// on the same stream, so the result the matmul stored into host memory is complete before it.
+static __global__ void host_status_kernel(const int* dev_status, int* host_status) {
+  *host_status = *dev_status;
+}
+
 static int32_t linear_host_enqueue(kanso_cuda_ctx* ctx, const kanso_cuda_weight* w, char* ph,
                                    char* pd, size_t xb, size_t xb_al, size_t yb, int64_t M,
                                    int32_t act_mode) {
   KANSO_CUDA_TRY(ctx, cudaMemcpyAsync(pd, ph, xb, cudaMemcpyHostToDevice, ctx->stream),
                  "linear_host: activations to device");
-  int32_t st = matmul_dispatch(ctx, w->dtype, w->dev, (const float*)pd, (float*)(pd + xb_al), M,
-                               w->rows, w->cols, act_mode);
+  // The batch-1..6 Q4_K GEMV writes every result element exactly once with a plain store and
+  // never reads y: it can store straight into the pinned host buffer (posted writes over PCIe,
+  // 16-57 KB), and a one-thread kernel passes the status word on, which leaves the graph one
+  // copy and two kernels instead of three copies and a kernel. Every other kernel (atomics onto
+  // a cleared y, several passes) keeps the device result and the copy back.
+  const bool direct_y = w->dtype == KANSO_DTYPE_Q4_K && act_mode == KANSO_ACT_F32 && M <= 6 &&
+                        w->cols % 256 == 0 && w->rows % 8 == 0 && w->rows >= 8;
+  float* yd = direct_y ? (float*)(ph + xb_al) : (float*)(pd + xb_al);
+  int32_t st = matmul_dispatch(ctx, w->dtype, w->dev, (const float*)pd, yd, M, w->rows, w->cols,
+                               act_mode);
   if (st) return st;
+  if (direct_y) {
+    host_status_kernel<<<1, 1, 0, ctx->stream>>>(ctx->dev_status, ctx->host_status);
+    return after_launch(ctx, "linear_host: status word");
+  }
   KANSO_CUDA_TRY(ctx,
                  cudaMemcpyAsync(ph + xb_al, pd + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream),
                  "linear_host: result to host");
