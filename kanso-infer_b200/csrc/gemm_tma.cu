@@ -314,12 +314,14 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
   // critical path, so scheduler 0 carries only that warp and the two loaders (one thread each,
   // mostly asleep on a barrier); the 16 dequantising warps sit on schedulers 1..3.
   const int pw = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int warp;  // role: 0..15 producer, 16 MMA issuer, 17 weight loader, 18 activation loader, 19 none
+  // role: 0..15 producer, 16 first MMA issuer, 17 weight loader, 18 activation loader, 19 none,
+  // 20 second MMA issuer
+  int warp;
   if ((pw & 3) == 0)
-    warp = (pw >> 2) < 3 ? 16 + (pw >> 2) : 19;
+    warp = (pw >> 2) < 3 ? 16 + (pw >> 2) : (pw >> 2) == 3 ? 20 : 19;
   else
     warp = (pw & 3) - 1 + 3 * (pw >> 2);
-  if (warp >= 16 && (pw & 3) != 0) warp = 19;
+  if (warp >= 16 && warp != 20 && (pw & 3) != 0) warp = 19;
   const int tid = warp * 32 + lane;
   const uint32_t unit_bytes = 32u * (uint32_t)a.Mt;
   const uint32_t bslot_bytes = (uint32_t)a.ub * unit_bytes;
@@ -335,14 +337,24 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
   uint64_t* acc_full = b_empty + TM_B_SLOTS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* issued_any = abort_flag + 1;  // [2]: did issuer i accumulate anything
 
   const int n0 = (int)blockIdx.x * TM_TILE_N;
   const int b0 = (int)((int64_t)a.boxes_total * blockIdx.y / a.ksplit);
   const int b1 = (int)((int64_t)a.boxes_total * (blockIdx.y + 1) / a.ksplit);
   // a chunk at the start of this CTA's range may need a scale or header from the box before it
   const int first = b0 > 0 ? b0 - 1 : 0;
-  uint32_t ncols = 32;
-  while (ncols < (uint32_t)a.Mt) ncols <<= 1;
+  // Up to 128 activation rows: two issuing threads, each with its own accumulator (even and
+  // odd stages), because a tcgen05.mma of few columns is bound by the issuing thread, not by the
+  // tensor core (measured: 8 MMAs + commit cost one thread 873 cycles at N = 32 whether or not a
+  // second thread issues beside it). The epilogue adds the two accumulators. With more rows a
+  // stage takes all four activation slots, so both threads would use every slot in turn and the
+  // second would have to wait for a slot's second filling without having seen its first (a
+  // parity wait cannot express that); those sizes are bound by the tensor core anyway.
+  const int nissue = a.Mt <= 128 ? 2 : 1;
+  uint32_t acc_cols = 32;
+  while (acc_cols < (uint32_t)a.Mt) acc_cols <<= 1;
+  const uint32_t ncols = acc_cols * (uint32_t)nissue;  // <= 512
 
   if (pw == 0) tmem_alloc(tmem_slot, ncols);
   if (threadIdx.x == 32) {
@@ -358,8 +370,9 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       mbar_init(&b_full[i], 1);
       mbar_init(&b_empty[i], 1);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, nissue);
     *abort_flag = 0;
+    issued_any[0] = issued_any[1] = 0;
     mbar_fence_init();
   }
   tc_fence_before();
@@ -440,12 +453,14 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
         raw_par ^= 1u;
       }
     }
-  } else if (warp == TM_PRODUCERS / 32) {
-    // ---- MMA issuer: one thread, and every instruction it executes sits on the critical
-    // path of the whole CTA, so the loop carries running descriptors and counters: no
-    // division, no address rebuilt from scratch ----
-    if (lane == 0) {
-      const bool two = a.Mt > 256;  // a second accumulator chunk of columns 256..
+  } else if (warp == TM_PRODUCERS / 32 || warp == 20) {
+    // ---- MMA issuers: one thread each, and every instruction they execute sits on the critical
+    // path of the stages they own, so a stage is straight-line code per slot size with every
+    // descriptor a constant offset from the stage's first. Issuer i owns the stages j = i,
+    // i + nissue, ...: A buffer j % 2 and the TMEM columns [i * acc_cols, i * acc_cols + Mt).
+    const int me = warp == 20 ? 1 : 0;
+    if (lane == 0 && me < nissue) {
+      const bool two = a.Mt > 256;  // a second chunk of columns 256.. (single issuer only)
       const uint32_t idesc0 = tc_idesc_f16(TM_TILE_N, two ? 256 : a.Mt);
       const uint32_t idesc1 = tc_idesc_f16(TM_TILE_N, two ? a.Mt - 256 : 16);
       const uint64_t adesc_buf0 = tc_smem_desc(smem_u32(As), TM_TILE_N * 16, 128);
@@ -453,115 +468,71 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
       const uint32_t a_kstep = (2u * (TM_TILE_N * 16)) >> 4;  // descriptor units per k-step of A
       const uint32_t b_unit = unit_bytes >> 4, b_slot = bslot_bytes >> 4;
       const uint32_t ub = (uint32_t)a.ub, row_bytes = (uint32_t)a.row_bytes;
-      uint32_t o = (uint32_t)b0 * TM_BOX_W;      // stream offset of the next chunk
-      uint32_t cm = ((uint32_t)b0 * 8u) % 9u;    // Q4_K: chunk index modulo 9, 0 = header
-      uint32_t bslot = 0, b_par = 0, in_grp = 0, acc = 0;
-      uint64_t bdesc = bdesc_base;
-      int abuf = 0;
-      uint32_t a_par = 0;
-      bool ok = true;
       const uint32_t adesc_hi = (uint32_t)(adesc_buf0 >> 32), bdesc_hi = (uint32_t)(bdesc_base >> 32);
       const uint32_t adesc_lo0 = (uint32_t)adesc_buf0, bdesc_lo0 = (uint32_t)bdesc_base;
-      for (int ss = SPB * (b1 - b0); ss > 0 && ok; --ss) {
+      const uint32_t acc_tmem = tmem_base + (uint32_t)me * acc_cols;
+      const uint32_t sps = 8u / ub;  // activation slots per stage (a stage is 8 k-steps)
+      const int nstages = SPB * (b1 - b0);
+      uint32_t acc = 0;
+      bool ok = true;
+      for (int j = me; j < nstages && ok; j += nissue) {
+        const uint32_t abuf = (uint32_t)j % TM_A_STAGES;
+        const uint32_t a_par = ((uint32_t)j / TM_A_STAGES) & 1u;
+        const uint32_t l0 = (uint32_t)j * sps;  // first activation slot group of the stage
         // the activations of a stage arrive long before its weights are dequantised: their
         // barrier is looked at first, so that one fence covers both waits
-        bool b_ready = false;
-        if (in_grp == 0) {
-          if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
-          b_ready = true;
-        }
+        if (!mbar_wait_bounded(&b_full[l0 % TM_B_SLOTS], (l0 / TM_B_SLOTS) & 1u)) ok = false;
         if (!mbar_wait_bounded(&a_full[abuf], a_par)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (o + CH * 16u <= row_bytes && in_grp == 0) {
-          // ---- a stage whose chunks all lie inside the row (every stage but the tail of a row
-          // whose length is not a multiple of the box): straight-line code per slot size, every
-          // descriptor a constant offset from the stage's first ----
-          const uint32_t alo = adesc_lo0 + (uint32_t)abuf * (TM_A_STAGE >> 4);
-          const uint32_t hdr = FMT == TM_FMT_Q4_K ? (cm == 0u ? 0u : 9u - cm) : 99u;  // chunk to skip
-          auto run = [&](auto ub_tag) {
-            constexpr int UB = decltype(ub_tag)::value;
+        const uint32_t chunk0 = (uint32_t)b0 * 8u + (uint32_t)j * CH;  // first chunk of the stage
+        const uint32_t o0 = chunk0 * 16u;
+        // chunks that are not weights: a Q4_K header (one in nine), bytes past the row's end
+        const uint32_t cm = FMT == TM_FMT_Q4_K ? chunk0 % 9u : 1u;
+        const uint32_t hdr = FMT == TM_FMT_Q4_K ? (cm == 0u ? 0u : 9u - cm) : 99u;
+        const uint32_t nvalid = o0 >= row_bytes ? 0u : min((uint32_t)CH, (row_bytes - o0 + 15u) >> 4);
+        const uint32_t alo = adesc_lo0 + abuf * (TM_A_STAGE >> 4);
+        auto run = [&](auto ub_tag) {
+          constexpr int UB = decltype(ub_tag)::value;
 #pragma unroll
-            for (int g = 0; g < CH * UPC / UB; ++g) {
-              if (g > 0 || !b_ready) {
-                if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
-                tc_fence_after();
-              }
-              uint32_t blo = bdesc_lo0 + bslot * b_slot;
-#pragma unroll
-              for (int u = 0; u < UB; ++u) {
-                const int ks = g * UB + u;
-                const bool skip = FMT == TM_FMT_Q4_K && (uint32_t)(ks / UPC) == hdr;
-                if (!skip && ok) {
-                  const uint64_t ad = tc_desc_join(alo + (uint32_t)ks * a_kstep, adesc_hi);
-                  const uint64_t bd = tc_desc_join(blo, bdesc_hi);
-                  tc_mma_f16(tmem_base, ad, bd, idesc0, acc);
-                  if (UB == 1 && two)
-                    tc_mma_f16(tmem_base + 256u, ad, tc_desc_join(blo + 256u, bdesc_hi), idesc1, acc);
-                  acc = 1;
-                }
-                blo += b_unit;
-              }
-              tc_commit(&b_empty[bslot]);
-              if (++bslot == TM_B_SLOTS) {
-                bslot = 0;
-                b_par ^= 1u;
-              }
+          for (int g = 0; g < CH * UPC / UB; ++g) {
+            const uint32_t l = l0 + (uint32_t)g, bslot = l % TM_B_SLOTS;
+            if (g > 0) {
+              if (!mbar_wait_bounded(&b_full[bslot], (l / TM_B_SLOTS) & 1u)) ok = false;
+              tc_fence_after();
             }
-          };
-          if (ub == 8u)
-            run(std::integral_constant<int, 8>{});
-          else if (ub == 4u)
-            run(std::integral_constant<int, 4>{});
-          else if (ub == 2u)
-            run(std::integral_constant<int, 2>{});
-          else
-            run(std::integral_constant<int, 1>{});
-          o += CH * 16u;
-          if (FMT == TM_FMT_Q4_K) cm = cm >= 5u ? cm - 5u : cm + 4u;
-        } else {
-          uint64_t adesc = adesc_buf0 + (uint64_t)((uint32_t)abuf * (TM_A_STAGE >> 4));
-#pragma unroll 1
-          for (int c = 0; c < CH; ++c) {
-            const bool valid = o < row_bytes && (FMT == TM_FMT_Q8_0 || cm != 0);
-#pragma unroll 1
-            for (int ks = 0; ks < UPC; ++ks) {
-              if (in_grp == 0) {
-                if (!b_ready) {
-                  if (!mbar_wait_bounded(&b_full[bslot], b_par)) ok = false;
-                  tc_fence_after();
-                }
-                b_ready = false;
-                bdesc = bdesc_base + (uint64_t)(bslot * b_slot);
-              }
-              if (valid && ok) {
-                tc_mma_f16(tmem_base, adesc, bdesc, idesc0, acc);
-                if (two) tc_mma_f16(tmem_base + 256u, adesc, bdesc + 256u, idesc1, acc);
+            uint32_t blo = bdesc_lo0 + bslot * b_slot;
+#pragma unroll
+            for (int u = 0; u < UB; ++u) {
+              const int ks = g * UB + u;
+              const uint32_t c = (uint32_t)(ks / UPC);
+              const bool skip = c == hdr || c >= nvalid;
+              if (!skip && ok) {
+                const uint64_t ad = tc_desc_join(alo + (uint32_t)ks * a_kstep, adesc_hi);
+                const uint64_t bd = tc_desc_join(blo, bdesc_hi);
+                tc_mma_f16(acc_tmem, ad, bd, idesc0, acc);
+                if (UB == 1 && two)
+                  tc_mma_f16(acc_tmem + 256u, ad, tc_desc_join(blo + 256u, bdesc_hi), idesc1, acc);
                 acc = 1;
               }
-              adesc += a_kstep;
-              bdesc += b_unit;
-              if (++in_grp == ub) {
-                tc_commit(&b_empty[bslot]);
-                in_grp = 0;
-                if (++bslot == TM_B_SLOTS) {
-                  bslot = 0;
-                  b_par ^= 1u;
-                }
-              }
+              blo += b_unit;
             }
-            o += 16u;
-            if (FMT == TM_FMT_Q4_K) cm = cm == 8u ? 0u : cm + 1u;
+            tc_commit(&b_empty[bslot]);
           }
-        }
+        };
+        if (ub == 8u)
+          run(std::integral_constant<int, 8>{});
+        else if (ub == 4u)
+          run(std::integral_constant<int, 4>{});
+        else if (ub == 2u)
+          run(std::integral_constant<int, 2>{});
+        else
+          run(std::integral_constant<int, 1>{});
         tc_commit(&a_empty[abuf]);
-        if (++abuf == TM_A_STAGES) {
-          abuf = 0;
-          a_par ^= 1u;
-        }
       }
+      issued_any[me] = acc;
       if (ok)
         tc_commit(acc_full);
       else
@@ -623,9 +594,20 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
     // own quarter, warp % 4), TMEM column = activation row
     const int q = pw & 3;
     const int64_t n = (int64_t)n0 + q * 32 + lane;
+    const bool any0 = issued_any[0] != 0, any1 = nissue == 2 && issued_any[1] != 0;
     for (int c16 = pw >> 2; c16 < a.Mt / 16; c16 += TM_THREADS / 128) {
       uint32_t r[16];
-      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) r[jj] = 0u;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16);
+      if (any0) tmem_ld16(taddr, r);
+      if (any1) {  // the second issuer's accumulator: the odd stages
+        uint32_t r1[16];
+        tmem_ld16(taddr + acc_cols, r1);
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj)
+          r[jj] = __float_as_uint(__uint_as_float(r[jj]) + __uint_as_float(r1[jj]));
+      }
       if (n < a.N) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
