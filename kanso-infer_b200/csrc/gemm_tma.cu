@@ -284,11 +284,14 @@ __device__ __forceinline__ bool tm_wait_polite(uint64_t* bar, uint32_t parity) {
 // looked at while the barrier is not ready, and it is set here when the wait runs out, so that
 // the CTA's other roles give up at their next poll.
 __device__ __forceinline__ bool tm_warp_wait(uint64_t* bar, uint32_t parity, int lane,
-                                             volatile uint32_t* abort_flag) {
+                                             volatile uint32_t* abort_flag,
+                                             uint64_t* bar2 = nullptr, uint32_t parity2 = 0) {
   (void)lane;
-  bool ok = false;
+  bool ok = false, ok1 = false, ok2 = bar2 == nullptr;
   for (uint32_t i = 0; i < (1u << 21); ++i) {
-    if (mbar_try_wait(bar, parity)) {
+    if (!ok1) ok1 = mbar_try_wait(bar, parity);
+    if (!ok2) ok2 = mbar_try_wait(bar2, parity2);
+    if (ok1 && ok2) {
       ok = true;
       break;
     }
@@ -395,13 +398,17 @@ __global__ void __launch_bounds__(TM_THREADS, 1)
     uint32_t ph = FMT == TM_FMT_Q8_0 ? (uint32_t)((64 * (int64_t)first + 16 * c) % 17)
                                      : (uint32_t)((8 * (int64_t)first + c) % 9);
     for (int box = first; box < b1; ++box) {
-      if (!tm_warp_wait(&raw_full[slot], raw_par, lane, abort_flag)) break;
+      // a box that will be dequantised: its arrival and the A buffer of its first stage are
+      // waited for in one poll loop (each wait costs a round trip even when it is complete)
+      if (!tm_warp_wait(&raw_full[slot], raw_par, lane, abort_flag,
+                        box >= b0 ? &a_empty[abuf] : nullptr, a_par))
+        break;
       const uint8_t* cur = Raw + slot * TM_BOX;
       const uint8_t* prev = Raw + prev_slot * TM_BOX;
       if (box >= b0) {
 #pragma unroll 1
         for (int st = 0; st < SPB; ++st) {
-          if (!tm_warp_wait(&a_empty[abuf], a_par, lane, abort_flag)) break;
+          if (st > 0 && !tm_warp_wait(&a_empty[abuf], a_par, lane, abort_flag)) break;
           uint8_t* dst = As + abuf * TM_A_STAGE + c * (4 * TM_TILE_N * 16) + row * 16;
           if (FMT == TM_FMT_Q8_0) {
             switch (ph) {
