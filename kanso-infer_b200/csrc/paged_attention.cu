@@ -513,9 +513,13 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
 
   // --- merge, by the CTA that draws the last ticket of this (sequence, kv head)
   __shared__ uint32_t s_last;
-  __threadfence();  // this CTA's partials are visible device-wide before its ticket is
+  // This CTA's partials must be visible device-wide before its ticket is drawn. One fence by
+  // the thread that draws it is enough: the block barrier orders every thread's stores before
+  // that thread, and its fence is cumulative over what it has observed (256 fences per CTA
+  // showed up as 0.47 membar stall cycles per issued instruction).
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     uint32_t* ticket = a.tickets + (size_t)seq * a.g.kv_heads + kvh;
     const uint32_t drawn = atomicAdd(ticket, 1u);
     s_last = drawn == np - 1;
