@@ -114,6 +114,16 @@ __device__ __forceinline__ void e4m3x4_to_f32(uint32_t w, float* f) {
   f[3] = b.y;
 }
 
+// Bytes of the first shared-memory region of stage 1: the partition's records, or the PV
+// reduction scratch [NT / (hd/8) slices][G][hd] f32 that later overlays them, whichever is larger.
+__host__ __device__ inline uint32_t pa_region0_bytes(uint32_t record_bytes, uint32_t G, uint32_t hd,
+                                                     uint32_t threads) {
+  uint32_t red = (threads / (hd / 8)) * G * hd * 4;
+  if (red < 128) red = 128;
+  const uint32_t r = record_bytes > red ? record_bytes : red;
+  return (r + 15u) & ~15u;
+}
+
 // NT = threads per CTA. FP8: the pool holds E4M3 bit patterns with power-of-two scales
 // (src/kv_cache/quantized_storage.rs:470-484); the query then stays in f32 and the products are
 // f32 multiply-adds on the exactly converted K and V values. Otherwise int8 with dp4a.
@@ -153,7 +163,10 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   // mbarrier, q planes, q scales, block ids, probabilities, reduction scratch
   const uint32_t max_blk = (a.part_tokens + bs - 1) / bs;
   uint8_t* tiles = smem;                                                    // 16-byte records
-  uint64_t* bar = reinterpret_cast<uint64_t*>(tiles + (size_t)max_blk * a.g.rec_bytes);
+  // The PV reduction scratch lies over the records: it is written only after every thread has
+  // finished reading them, and the region is sized for the larger of the two.
+  uint64_t* bar = reinterpret_cast<uint64_t*>(
+      tiles + pa_region0_bytes(max_blk * a.g.rec_bytes, G, hd, NT));
   int8_t* qhi = reinterpret_cast<int8_t*>(bar + 2);          // [G][hd]
   int8_t* qlo = qhi + G * hd;                                // [G][hd]
   float* qf = reinterpret_cast<float*>(qhi);                 // FP8: [G][hd] f32 instead of the planes
@@ -161,7 +174,7 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   uint32_t* blk = reinterpret_cast<uint32_t*>(qd + PA_MAX_GROUP);  // [part_tokens/bs + 1]
   const uint32_t nblk_part = (max_blk + 4) & ~3u;
   float* prob = reinterpret_cast<float*>(blk + nblk_part);   // [G][part_tokens]
-  float* red = prob + ((G * a.part_tokens + 3) & ~3u);       // PV scratch, 16-byte aligned
+  float* red = reinterpret_cast<float*>(tiles);              // PV scratch (see above)
 
   // physical blocks of this partition (bounds-checked once); partitions start on a block
   const uint32_t nb = (n + bs - 1) / bs;
@@ -469,6 +482,7 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     }
   }
   // reduce over token slices through shared memory: red[slice][G][hd]
+  __syncthreads();  // every thread is done with the records the scratch overlays
   float4* red4 = reinterpret_cast<float4*>(red);
 #pragma unroll
   for (int gq = 0; gq < G; ++gq) {
@@ -625,13 +639,37 @@ static size_t pa_stage1_smem(uint32_t G, uint32_t hd, uint32_t pt, uint32_t bloc
                              uint32_t rec_bytes, uint32_t threads, bool fp8 = false) {
   const uint32_t max_blk = (pt + block_size - 1) / block_size;
   const uint32_t nblk_part = (max_blk + 4) & ~3u;
-  const uint32_t dwords = hd / 8, nslice = threads / dwords;
-  size_t smem = (size_t)max_blk * rec_bytes + 16 + (fp8 ? 4 : 2) * G * hd + PA_MAX_GROUP * 4 +
-                nblk_part * 4 +
-                (size_t)((G * pt + 3) & ~3u) * 4;
-  size_t red_bytes = (size_t)nslice * G * hd * 4;
-  if (red_bytes < 128) red_bytes = 128;
-  return smem + red_bytes;
+  return (size_t)pa_region0_bytes(max_blk * rec_bytes, G, hd, threads) + 16 +
+         (fp8 ? 4 : 2) * G * hd + PA_MAX_GROUP * 4 + nblk_part * 4 +
+         (size_t)((G * pt + 3) & ~3u) * 4 + 16;
+}
+
+// Tokens per context partition. Enough CTAs to cover the SMs, but no smaller than 64 tokens; the
+// partition's records are staged in shared memory, so the size also decides how many CTAs share
+// an SM: with plenty of CTAs (large batches) the largest whole-block size that lets THREE CTAs
+// fit is taken (measured on 64 sequences of 256..4096 tokens, 5 kv heads x 3 query heads:
+// 512 tokens = two CTAs per SM 61.0 us, 448 = three 54.6 us, 384 57.4 us, 256 67.1 us), else two.
+static uint32_t pa_partition_tokens(const kanso_cuda_ctx* ctx, const kanso_paged_attention_params* p,
+                                    const KvGeom& g, uint64_t cap) {
+  const uint32_t G = p->num_heads / p->num_kv_heads, hd = p->head_dim, bs = p->block_size;
+  auto smem_of = [&](uint32_t pt) {
+    return pa_stage1_smem(G, hd, pt, bs, g.rec_bytes, pa_threads(pt), g.fp8 != 0);
+  };
+  uint32_t pt = 512;
+  while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
+                        (uint64_t)ctx->sm_count / 2)
+    pt >>= 1;
+  while (pt > 64 && smem_of(pt) > (size_t)ctx->smem_optin / 2) pt >>= 1;
+  if (pt % bs) pt = ((pt + bs - 1) / bs) * bs;  // a partition starts on a block record
+  if (pt == 512 && bs <= 64) {
+    // 2.5 KB per CTA for the kernel's static arrays and the driver's reserve
+    const size_t budget = (size_t)ctx->smem_per_sm / 3 - 2560;
+    uint32_t pt3 = 512 / bs * bs;
+    while (pt3 > 256 && smem_of(pt3) > budget) pt3 -= bs;
+    const uint64_t ctas3 = (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt3 - 1) / pt3);
+    if (pt3 >= 384 && smem_of(pt3) <= budget && ctas3 >= 6ull * ctx->sm_count) pt = pt3;
+  }
+  return pt;
 }
 
 template <int G, int NT, bool FP8>
@@ -686,19 +724,9 @@ int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv
   KvGeom g = kv_geom(kv);
   const uint32_t G = p->num_heads / p->num_kv_heads;
   const uint32_t hd = p->head_dim;
-  // partition size: enough CTAs to cover the SMs, but no smaller than 64 tokens
   uint64_t cap = (uint64_t)p->max_num_blocks_per_seq * p->block_size;
   if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
-  uint32_t pt = 512;
-  while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
-                        (uint64_t)ctx->sm_count / 2)
-    pt >>= 1;
-  // the partition's records are staged in shared memory: two CTAs per SM when possible
-  while (pt > 64 &&
-         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0) > (size_t)ctx->smem_optin / 2)
-    pt >>= 1;
-  // whole blocks per partition: a partition starts on a block record
-  if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
+  const uint32_t pt = pa_partition_tokens(ctx, p, g, cap);
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
   const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
   const size_t acc_bytes = nheads_total * nparts * hd * sizeof(float);
@@ -946,14 +974,7 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   const uint32_t hd = p->head_dim;
   uint64_t cap = (uint64_t)p->max_num_blocks_per_seq * p->block_size;
   if (max_ctx_hint && max_ctx_hint < cap) cap = max_ctx_hint;
-  uint32_t pt = 512;
-  while (pt > 64 && (uint64_t)p->num_seqs * p->num_kv_heads * ((cap + pt - 1) / pt) <
-                        (uint64_t)ctx->sm_count / 2)
-    pt >>= 1;
-  while (pt > 64 &&
-         pa_stage1_smem(G, hd, pt, p->block_size, g.rec_bytes, pa_threads(pt), g.fp8 != 0) > (size_t)ctx->smem_optin / 2)
-    pt >>= 1;
-  if (pt % p->block_size) pt = ((pt + p->block_size - 1) / p->block_size) * p->block_size;
+  const uint32_t pt = pa_partition_tokens(ctx, p, g, cap);
   const uint32_t nparts = (uint32_t)((cap + pt - 1) / pt);
 
   const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
