@@ -179,6 +179,13 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     step_bytes = args.pairs * (alg_bytes(*UP) + alg_bytes(*DOWN))
     val = args.steps * step_bytes / dt / 1e9
+    workload = "cfg2 Q4_K GEMV batch 1: W_up[14336x4096] + W_down[4096x14336]"
+    if args.gpus > 1:
+        # the GPU arm's weak-scaling step holds this same ring of pairs PER GPU (one shard of the
+        # N-times-larger FFN pair each); the host has one set of cores, so it is timed on one
+        # GPU's share: the same bytes per pair, GB/s comparable per byte
+        workload = (f"one GPU's share of the sharded FFN pair (W_up[{args.gpus * UP[0]}x{UP[1]}] by "
+                    f"rows, W_down[{DOWN[0]}x{args.gpus * DOWN[1]}] along K): " + workload)
     sample = (f"each step = the ring of {args.pairs} (up, down) pairs, every GEMV's rows split over "
               f"{cores} threads; the reference's own loop is single-threaded")
     print(json.dumps({
@@ -186,8 +193,8 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "cfg2 Q4_K GEMV batch 1: W_up[14336x4096] + W_down[4096x14336]",
-                   "ring_pairs": args.pairs, "bytes_per_step": step_bytes},
+        "config": {"workload": workload, "ring_pairs": args.pairs,
+                   "bytes_per_step": step_bytes},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
