@@ -59,6 +59,28 @@ def test_batched_matmul_at_config_shapes(ctx, kb, oracle, torch_cuda, fmt, N, M)
     assert err <= TOL, f"{fmt} M={M} N={N}: {err:.2e}"
 
 
+@pytest.mark.parametrize("M", [2, 3, 5, 7])
+def test_q8_0_few_rows_take_the_tensor_core_gemm(ctx, kb, oracle, torch_cuda, M):
+    """Q8_0 matrices whose rows start on 16-byte boundaries go to the TMA-staged GEMM from two
+    activation rows on (below nine rows the int8-MMA GEMV used to take them): same bound, and the
+    rows beyond M of the 16-row accumulator tile must not leak into y."""
+    torch = torch_cuda
+    N = 4096
+    rows2d, W = quantized(oracle, kb, ctx, "q8_0", N)
+    rng = np.random.Generator(np.random.PCG64(0xB2000350 + M))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    guard = torch.full((M + 1, N), float("nan"), dtype=torch.float32, device="cuda")
+    y = guard[:M]
+    W.forward(dev(torch, x), y, M)
+    ctx.sync()
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert torch.isnan(guard[M]).all()  # nothing was written past the M rows
+    pick = sample_rows(rng, N)
+    ref = oracle.gemm_q8_0(np.ascontiguousarray(rows2d[pick]).reshape(-1), x, M, pick.size, K)
+    assert float(np.max(np.abs(got[:, pick] - ref))) / float(np.max(np.abs(got))) <= TOL
+
+
 @pytest.mark.parametrize("M", [8, 32, 128])
 def test_q8_activation_mode_at_config_shapes(ctx, kb, oracle, torch_cuda, M):
     """KANSO_ACT_Q8: activations quantised per 32 by quantize_row_q8_0 and integer-dotted
