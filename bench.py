@@ -398,12 +398,17 @@ def decode_legs(torch, kb, O, ctx, stream, batches=(1, 8, 32, 64), check=True):
     todo = list(batches)
     if check and 8 not in todo:
         todo.append(8)
-    for B in sorted(set(todo), key=lambda b: (b != 8, b)):  # the checked batch first
+    # (batch, fp8 pool?): every batch on the int8 pool, then batch 8 (checked) and the largest
+    # batch on the fp8 pool (E4M3 bytes, power-of-two scales)
+    runs = [(B, False) for B in sorted(set(todo), key=lambda b: (b != 8, b))]  # checked batch first
+    if check:
+        runs += [(8, True)] + ([(max(batches), True)] if max(batches) != 8 else [])
+    for B, fp8 in runs:
         lens = rng.integers(256, 4097, size=B)
         nblk = [(int(c) + bs - 1) // bs for c in lens]
         NB = sum(nblk) + 8
-        pool = kb.KvPool(ctx, L, NB, bs, KH, hd)
-        opool = O.KvPool(L, NB, bs, KH, hd) if (check and B == 8) else None
+        pool = kb.KvPool(ctx, L, NB, bs, KH, hd, kb.KV_FP8 if fp8 else kb.KV_INT8)
+        opool = O.KvPool(L, NB, bs, KH, hd, fp8=fp8) if (check and B == 8) else None
         perm = rng.permutation(NB)
         maxb = max(nblk)
         tables = np.zeros((B, maxb), np.uint32)
@@ -441,12 +446,12 @@ def decode_legs(torch, kb, O, ctx, stream, batches=(1, 8, 32, 64), check=True):
             err = float(np.max(np.abs(logits_h - ref)))
             same = [int(np.argmax(r)) for r in logits_h] == [O.greedy_token(r) for r in ref]
             if st != 0 or not err <= 1e-2 or not same:
-                raise SystemExit(f"bench: cfg4 B=8 differs from the oracle engine: max |dlogit| "
+                raise SystemExit(f"bench: cfg4 B=8 (fp8 pool: {fp8}) differs from the oracle engine: max |dlogit| "
                                  f"{err:.2e}, same greedy tokens {same}")
             entry["check_vs_oracle_max_abs_dlogit"] = err
             # the step above stored the newest token: write a fresh history row over it so that
             # the timed steps below see the same state as the other batches
-        if B in batches:
+        if B in batches or fp8:
             tok, pos, slot = (torch.from_numpy(a.astype(np.int32)).cuda()
                               for a in (tok_h, pos_h, slot_h))
             tb = torch.from_numpy(tables.astype(np.int32)).cuda()
@@ -475,7 +480,7 @@ def decode_legs(torch, kb, O, ctx, stream, batches=(1, 8, 32, 64), check=True):
                           "e2e_host_call": {"us_per_step": e2e_us, "tok/s": B / e2e_us * 1e6,
                                             "h2d_bytes": int(4 * (4 * B + B * maxb)),
                                             "d2h_bytes": int(4 * B * vocab)}})
-        out[f"B{B}"] = entry
+        out[f"B{B}_fp8_pool" if fp8 else f"B{B}"] = entry
         pool.destroy()
     m.destroy()
     return out
