@@ -486,6 +486,101 @@ def decode_legs(torch, kb, O, ctx, stream, batches=(1, 8, 32, 64), check=True):
     return out
 
 
+def prefill_attention_leg(torch, kb, O, ctx, stream):
+    """Chunked-prefill attention over the int8 pool (SmolLM2-360M heads: 15 query / 5 KV heads of
+    64, 16-token blocks, permuted tables). First a small mixed batch (a 48-token chunk on 80 cached
+    tokens and a whole 33-token prompt) against the oracle's restatement of the reference's masked
+    dense attention, then 4 sequences with 512-token chunks on 1536 cached tokens each, timed over
+    three layers of records (3 x 28 MB of cache, contexts walked once per query row)."""
+    H, KH, hd, bs = 15, 5, 64, 16
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    rng = np.random.Generator(np.random.PCG64(SEED + 60))
+
+    def build(ctx_lens, layers, with_oracle):
+        nblk = [(c + bs - 1) // bs for c in ctx_lens]
+        NB = sum(nblk) + 4
+        perm = rng.permutation(NB)
+        maxb = max(nblk)
+        tab = np.zeros((len(ctx_lens), maxb), np.uint32)
+        u = 0
+        for i, nb in enumerate(nblk):
+            tab[i, :nb] = perm[u:u + nb]
+            tab[i, nb:] = tab[i, nb - 1]
+            u += nb
+        pool = kb.KvPool(ctx, layers, NB, bs, KH, hd)
+        opool = O.KvPool(layers, NB, bs, KH, hd) if with_oracle else None
+        for i, c in enumerate(ctx_lens):
+            t = np.arange(c)
+            slots = (tab[i][t // bs] * bs + t % bs).astype(np.uint32)
+            sd = torch.from_numpy(slots.astype(np.int64)).to(torch.int32).cuda()
+            for l in range(layers):
+                k = rng.standard_normal((c, KH * hd), dtype=np.float32)
+                v = rng.standard_normal((c, KH * hd), dtype=np.float32)
+                pool.write_slots(l, sd, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), c)
+                if opool is not None:
+                    opool.write_slots(l, slots, k, v)
+        return pool, opool, tab, maxb
+
+    # check
+    seqs = [(80, 48), (0, 33)]
+    ctx_lens = [a + b for a, b in seqs]
+    pool, opool, tab, maxb = build(ctx_lens, 1, True)
+    T = sum(b for _, b in seqs)
+    q = rng.standard_normal((T, H * hd), dtype=np.float32)
+    out = torch.empty(T, H * hd, device="cuda")
+    p = kb.PagedAttentionParams(len(seqs), H, KH, hd, bs, maxb, scale)
+    pool.paged_attention_prefill(0, torch.from_numpy(q).cuda(), torch.from_numpy(tab.reshape(-1).astype(np.int32)).cuda(),
+                                 np.array(ctx_lens, np.uint32), np.array([b for _, b in seqs], np.uint32),
+                                 out, p)
+    ctx.sync()
+    got = out.cpu().numpy()
+    err, row = 0.0, 0
+    for i, (sp, ql) in enumerate(seqs):
+        nb = (ctx_lens[i] + bs - 1) // bs
+        st, ref = O.prefill_attention_int8(opool, 0, q[row:row + ql], tab[i, :nb], sp, H, scale)
+        err = max(err, float(np.max(np.abs(got[row:row + ql] - ref)) / np.max(np.abs(ref))))
+        row += ql
+    if not err <= 1e-3:
+        raise SystemExit(f"bench: prefill attention differs from the oracle: {err:.2e}")
+    pool.destroy()
+    # timing
+    S, chunk, cached, layers = 4, 512, 1536, 3
+    ctx_lens = [cached + chunk] * S
+    pool, _, tab, maxb = build(ctx_lens, layers, False)
+    T = S * chunk
+    qd = torch.randn(T, H * hd, device="cuda")
+    out = torch.empty(T, H * hd, device="cuda")
+    td = torch.from_numpy(tab.reshape(-1).astype(np.int32)).cuda()
+    p = kb.PagedAttentionParams(S, H, KH, hd, bs, maxb, scale)
+    cl, ql = np.array(ctx_lens, np.uint32), np.full(S, chunk, np.uint32)
+
+    def step():
+        for l in range(layers):
+            pool.paged_attention_prefill(l, qd, td, cl, ql, out, p)
+    # the call builds per-call row arrays on the host, so it is timed as plain launches (it
+    # refuses to be captured in a graph)
+    for _ in range(3):
+        step()
+    ctx.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 10
+    e0.record(stream)
+    for _ in range(iters):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (iters * layers)
+    # every query row walks its causal prefix: the records one launch touches, counted per row
+    row_tokens = sum(int(c) - chunk + i + 1 for c in ctx_lens for i in range(chunk))
+    flops = 4.0 * row_tokens * H * hd  # QK and PV
+    res = {"check_vs_oracle_rel_err": err, "sequences": S, "chunk": chunk, "cached": cached,
+           "us_per_launch": us, "query_rows_per_s": T / us * 1e6,
+           "cache_GB/s_per_row_walk": row_tokens * KH * (2 * hd + 8) / us / 1e3,
+           "GFLOP/s": flops / us / 1e3}
+    pool.destroy()
+    return res
+
+
 def other_paths(torch, kb, O, ctx, stream, decode_batches=(1, 8, 32, 64), decode_only=False):
     """The other rows of the hot path, timed the same way as the headline (captured graph, CUDA
     events, weights rotated through more than the L2's 126 MB) and checked against the oracle
@@ -495,6 +590,7 @@ def other_paths(torch, kb, O, ctx, stream, decode_batches=(1, 8, 32, 64), decode
                                                               decode_batches, check=False)}
     return {"gemv": gemv_legs(torch, kb, ctx, stream),
             "cfg3_batched_gemm": gemm_legs(torch, kb, O, ctx, stream),
+            "prefill_attention": prefill_attention_leg(torch, kb, O, ctx, stream),
             "cfg4_decode_smollm2_360m_q8_0": decode_legs(torch, kb, O, ctx, stream, decode_batches)}
 
 

@@ -346,7 +346,9 @@ int32_t kanso_cuda_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
  * offset causal mask of -1e9 leaves (src/model.rs:1027-1043). q and out f32
  * [sum of query_lens, num_heads*head_dim], rows in sequence order; block_tables device
  * u32[num_seqs*max_blocks]; the two length arrays are HOST arrays (they are host slices in the
- * reference's forward_batch, src/model.rs:1360-1369). */
+ * reference's forward_batch, src/model.rs:1360-1369). Not capturable in a CUDA graph (the
+ * per-row arrays are built on the host for each call): KANSO_ERR_UNSUPPORTED while the context's
+ * stream is being captured. */
 int32_t kanso_cuda_paged_attention_prefill(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv,
                                            uint32_t layer, const float* q,
                                            const uint32_t* block_tables,

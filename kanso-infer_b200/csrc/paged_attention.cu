@@ -867,6 +867,14 @@ int32_t kanso_cuda_paged_attention_prefill(kanso_cuda_ctx* ctx, const kanso_cuda
   if (hd < 16 || (hd & (hd - 1)) != 0)
     return fail(ctx, KANSO_ERR_UNSUPPORTED,
                 "paged attention: head_dim %u is not one of 16, 32, 64, 128, 256", hd);
+  // The per-row arrays are built here on the host for this call's lengths and copied from a
+  // temporary: a captured graph would replay the copy from memory that no longer exists.
+  cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &cap_st) == cudaSuccess &&
+      cap_st != cudaStreamCaptureStatusNone)
+    return fail(ctx, KANSO_ERR_UNSUPPORTED,
+                "paged_attention_prefill cannot be captured in a CUDA graph (its row arrays are "
+                "per-call host data)");
   const uint64_t cap = (uint64_t)params->max_num_blocks_per_seq * params->block_size;
   std::vector<uint32_t> rows;  // [row_seq | row_ctx]
   uint64_t T = 0;

@@ -56,3 +56,35 @@ def test_prefill_attention_matches_oracle(ctx, kb, oracle, torch_cuda, H, KH, hd
                                        np.array([ql for _, ql in seqs], np.uint32), out, p)
         assert e.value.code == kb.ERR_SHAPE
     gp.destroy()
+
+
+def test_prefill_attention_refuses_graph_capture(kb, oracle, torch_cuda):
+    """The call builds its per-row arrays on the host for each call, so a captured graph would
+    replay a copy from memory that is gone: while the stream is being captured it must enqueue
+    nothing and say so."""
+    torch = torch_cuda
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = kb.Context(0, stream)
+        H, KH, hd, bs = 4, 2, 64, 16
+        gp = kb.KvPool(ctx, 1, 8, bs, KH, hd)
+        q = torch.zeros((5, H * hd), device="cuda")
+        out = torch.zeros_like(q)
+        tab = torch.zeros(4, dtype=torch.int32, device="cuda")
+        p = kb.PagedAttentionParams(1, H, KH, hd, bs, 4, 0.125)
+        ctx.sync()
+        seen = None
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            try:
+                gp.paged_attention_prefill(0, q, tab, np.array([5], np.uint32),
+                                           np.array([5], np.uint32), out, p)
+            except kb.KansoError as e:
+                seen = e.code
+        assert seen == kb.ERR_UNSUPPORTED
+        # outside a capture the same call works
+        gp.paged_attention_prefill(0, q, tab, np.array([5], np.uint32), np.array([5], np.uint32),
+                                   out, p)
+        ctx.sync()
+        gp.destroy()
+        ctx.close()
