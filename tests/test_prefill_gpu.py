@@ -58,6 +58,7 @@ def test_prefill_attention_matches_oracle(ctx, kb, oracle, torch_cuda, H, KH, hd
     gp.destroy()
 
 
+@pytest.mark.filterwarnings("ignore:The CUDA Graph is empty")  # that is the point: nothing enqueued
 def test_prefill_attention_refuses_graph_capture(kb, oracle, torch_cuda):
     """The call builds its per-row arrays on the host for each call, so a captured graph would
     replay a copy from memory that is gone: while the stream is being captured it must enqueue
