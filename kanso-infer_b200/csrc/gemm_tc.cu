@@ -21,12 +21,10 @@
 //     16-byte core-matrix rows (no swizzle: 8 rows x 16 bytes per core matrix, K-adjacent matrices
 //     2 KB apart), double-buffered;
 //   * a 17th warp fetches the activation tile of the stage with one cp.async.bulk, and its
-//     elected lane issues the wh*xh tcgen05.mma instructions (M=128, N=Mt, K=16, kind::f16, f32
-//     accumulate in TMEM); an 18th warp's elected lane issues the two cross terms into a second
-//     accumulator (the instruction is bound by its issuing thread at these widths); both commit
-//     to per-buffer mbarriers, which frees the stage;
-//   * after the last stage the producer warps read both accumulators with tcgen05.ld (lane =
-//     weight row, column = activation row), add them and write y (optionally adding a residual); with split-K the
+//     elected lane issues the tcgen05.mma instructions (M=128, N=Mt, K=16, kind::f16, f32
+//     accumulate in TMEM) and commits them to per-buffer mbarriers, which frees the stage;
+//   * after the last stage the producer warps read the accumulator with tcgen05.ld (lane = weight
+//     row, column = activation row) and write y (optionally adding a residual); with split-K the
 //     partial sums are added with atomics (y is cleared by the pack kernel).
 // Several matrices that share their activations (Q/K/V, gate/up) run as one launch.
 // Every mbarrier wait is bounded; on a timeout the CTA records DEV_WAIT_TIMEOUT, frees its
@@ -45,7 +43,7 @@
 namespace kanso {
 
 constexpr int TC_PRODUCERS = 512;           // threads that copy, dequantise and run the epilogue
-constexpr int TC_THREADS = TC_PRODUCERS + 64;  // plus two warps that issue the MMAs
+constexpr int TC_THREADS = TC_PRODUCERS + 32;  // plus one warp that issues the MMAs
 constexpr int TC_MAX_SEGS = 3;   // matrices of one launch that share the activations (Q, K, V)
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
@@ -367,18 +365,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   const int64_t N = a.N[sg];
   const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
   const int s1 = (int)((int64_t)a.stages_total * (blockIdx.y + 1) / a.ksplit);
-  // Two issuing threads, an accumulator each: the first issues wh*xh, the second the two cross
-  // terms wl*xh and wh*xl, and the epilogue adds the accumulators. A tcgen05.mma of this width is
-  // bound by its issuing thread (about 86 cycles each, whatever a second thread does beside
-  // it), and a stage has twelve of them.
-  uint32_t acc_cols = 32;
-  while (acc_cols < (uint32_t)a.Mt) acc_cols <<= 1;  // Mt <= 128
-  const uint32_t ncols = 2 * acc_cols;
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)a.Mt) ncols <<= 1;
 
   if (warp == 0) tmem_alloc(tmem_slot, ncols);
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
-      mbar_init(&done[i], 2);  // both issuers commit a buffer's MMAs
+      mbar_init(&done[i], 1);
       mbar_init(&full[i], TC_PRODUCERS / 32);  // one arrival per producer warp
       mbar_init(&bfull[i], 1);
     }
@@ -435,43 +428,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else if (warp == TC_PRODUCERS / 32 + 1) {
-    if (lane == 0) {
-      // second issuer: the cross terms of every k-step into the second accumulator; it waits on
-      // the same barriers (both tiles of the buffer), the first issuer moves the B tiles
-      const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
-      const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;
-      const uint32_t acc1 = tmem_base + acc_cols;
-      int buf = 0;
-      uint32_t par = 0;
-      for (int s = s0; s < s1; ++s) {
-        const int it = s - s0;
-        if (!mbar_wait_bounded(&full[buf], par) || !mbar_wait_bounded(&bfull[buf], par)) {
-          *abort_flag = 1;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(As + buf * TC_A_STAGE);
-        const uint32_t b_addr = smem_u32(Bs + buf * b_stage);
-        const uint64_t ah0 = tc_smem_desc(a_addr, TC_TILE_N * 16, 128);
-        const uint64_t al0 = tc_smem_desc(a_addr + TC_A_PLANE, TC_TILE_N * 16, 128);
-        const uint64_t bh0 = tc_smem_desc(b_addr, a.Mt * 16, 128);
-        const uint64_t bl0 = tc_smem_desc(b_addr + b_plane, a.Mt * 16, 128);
-#pragma unroll
-        for (int j = 0; j < TC_KC / 16; ++j) {
-          const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
-          const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
-          tc_mma_f16(acc1, al, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wl * xh
-          tc_mma_f16(acc1, ah, bl, idesc, 1u);                            // wh * xl
-        }
-        tc_commit(&done[buf]);
-        if (++buf == NS) {
-          buf = 0;
-          par ^= 1;
-        }
-      }
-    }
-    __syncwarp();
   } else {
     if (lane == 0) {
       // B tiles by bulk copy, then the MMAs
@@ -496,12 +452,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         const uint32_t a_addr = smem_u32(As + buf * TC_A_STAGE);
         const uint32_t b_addr = smem_u32(Bs + buf * b_stage);
         const uint64_t ah0 = tc_smem_desc(a_addr, TC_TILE_N * 16, 128);
+        const uint64_t al0 = tc_smem_desc(a_addr + TC_A_PLANE, TC_TILE_N * 16, 128);
         const uint64_t bh0 = tc_smem_desc(b_addr, a.Mt * 16, 128);
+        const uint64_t bl0 = tc_smem_desc(b_addr + b_plane, a.Mt * 16, 128);
 #pragma unroll
         for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
-          const uint64_t ah = ah0 + (uint64_t)(j * a_k);
-          const uint64_t bh = bh0 + (uint64_t)(j * b_k);
+          const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
+          const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
           tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
+          tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
+          tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
         }
         tc_commit(&done[buf]);
         // B of stage s+NS-1 goes where the MMAs of stage s-1 read: wait for those (issued one
@@ -536,17 +496,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     const int q = warp & 3;
     const int64_t n = n0 + q * 32 + lane;
     for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TC_PRODUCERS / 128) {
-      uint32_t r[16], r1[16];
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16);
-      tmem_ld16(taddr, r);
-      tmem_ld16(taddr + acc_cols, r1);  // the cross terms
+      uint32_t r[16];
+      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
       if (n < N) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
           const int m = c16 * 16 + jj;
           if (m < a.M) {
             float* dst = a.y[sg] + (int64_t)m * N + n;
-            const float v = __uint_as_float(r[jj]) + __uint_as_float(r1[jj]);
+            const float v = __uint_as_float(r[jj]);
             if (a.ksplit == 1)
               *dst = a.resid ? a.resid[(int64_t)m * N + n] + v : v;
             else
