@@ -20,12 +20,15 @@
 //     int8 -> f16 by byte permute; Q4_K: (d*sc)*q - dmin*m in f32) into f16 hi/lo terms and store
 //     16-byte core-matrix rows (no swizzle: 8 rows x 16 bytes per core matrix, K-adjacent matrices
 //     2 KB apart), double-buffered;
-//   * a 17th warp fetches the activation tile of the stage with one cp.async.bulk, and its
-//     elected lane issues the tcgen05.mma instructions (M=128, N=Mt, K=16, kind::f16, f32
-//     accumulate in TMEM) and commits them to per-buffer mbarriers, which frees the stage;
-//   * after the last stage the producer warps read the accumulator with tcgen05.ld (lane = weight
-//     row, column = activation row) and write y (optionally adding a residual); with split-K the
-//     partial sums are added with atomics (y is cleared by the pack kernel).
+//   * one thread of a 19th warp fetches the activation tile of every stage with one
+//     cp.async.bulk; the elected lanes of a 17th and an 18th warp issue the tcgen05.mma
+//     instructions (M=128, N=Mt, K=16, kind::f16, f32 accumulate in TMEM) of the even and of the
+//     odd stages, each into an accumulator of its own (the instruction is bound by its issuing
+//     thread at these widths), and commit them to the stage's mbarrier, which frees its buffers;
+//   * after the last stage the producer warps read both accumulators with tcgen05.ld (lane =
+//     weight row, column = activation row), add them and write y (optionally adding a
+//     residual); with split-K the partial sums are added with atomics (y is cleared by the pack
+//     kernel).
 // Several matrices that share their activations (Q/K/V, gate/up) run as one launch.
 // Every mbarrier wait is bounded; on a timeout the CTA records DEV_WAIT_TIMEOUT, frees its
 // TMEM columns and returns.
@@ -43,7 +46,7 @@
 namespace kanso {
 
 constexpr int TC_PRODUCERS = 512;           // threads that copy, dequantise and run the epilogue
-constexpr int TC_THREADS = TC_PRODUCERS + 32;  // plus one warp that issues the MMAs
+constexpr int TC_THREADS = TC_PRODUCERS + 96;  // plus two warps that issue the MMAs and one that loads B
 constexpr int TC_MAX_SEGS = 3;   // matrices of one launch that share the activations (Q, K, V)
 constexpr int TC_KC = 64;        // K values per stage
 constexpr int TC_TILE_N = 128;   // weight rows per CTA = MMA M
@@ -365,13 +368,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   const int64_t N = a.N[sg];
   const int s0 = (int)((int64_t)a.stages_total * blockIdx.y / a.ksplit);
   const int s1 = (int)((int64_t)a.stages_total * (blockIdx.y + 1) / a.ksplit);
-  uint32_t ncols = 32;
-  while (ncols < (uint32_t)a.Mt) ncols <<= 1;
+  // Two issuing threads with an accumulator each take the stages in turn (even / odd) and the
+  // epilogue adds the accumulators: a tcgen05.mma of this width is bound by its issuing thread
+  // (about 86 cycles each, whatever a second thread does beside it), and a stage has twelve.
+  uint32_t acc_cols = 32;
+  while (acc_cols < (uint32_t)a.Mt) acc_cols <<= 1;  // Mt <= 128
+  const uint32_t ncols = 2 * acc_cols;
 
   if (warp == 0) tmem_alloc(tmem_slot, ncols);
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
-      mbar_init(&done[i], 1);
+      mbar_init(&done[i], 1);  // the commit of the issuer that owns the stage
       mbar_init(&full[i], TC_PRODUCERS / 32);  // one arrival per producer warp
       mbar_init(&bfull[i], 1);
     }
@@ -428,22 +435,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else {
+  } else if (warp == TC_PRODUCERS / 32 + 2) {
     if (lane == 0) {
-      // B tiles by bulk copy, then the MMAs
-      const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
-      const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;  // per 16 k
+      // ---- B tiles (packed activations) by bulk copy, one stage per shared-memory buffer; a
+      // buffer is refilled once the MMAs of the stage that used it last have retired
       const uint8_t* bsrc = reinterpret_cast<const uint8_t*>(a.xp);
-      auto copy_b = [&](int s, int b) {
-        mbar_arrive_expect_tx(&bfull[b], b_stage);
-        bulk_g2s(Bs + b * b_stage, bsrc + (size_t)s * b_stage, b_stage, &bfull[b]);
-      };
-      pdl_wait();
-      for (int i = 0; i < NS - 1 && s0 + i < s1; ++i) copy_b(s0 + i, i);
-      int buf = 0, prev = NS - 1;  // prev = buffer of stage s - 1 = buffer of stage s + NS - 1
-      uint32_t par = 0, prev_par = 1;
+      pdl_wait();  // the pack kernel has written the activations
+      int buf = 0;
+      uint32_t reuse_par = 1;
       for (int s = s0; s < s1; ++s) {
         const int it = s - s0;
+        if ((it >= NS && !mbar_wait_bounded(&done[buf], reuse_par)) || *abort_flag) {
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(&bfull[buf], b_stage);
+        bulk_g2s(Bs + buf * b_stage, bsrc + (size_t)s * b_stage, b_stage, &bfull[buf]);
+        if (++buf == NS) {
+          buf = 0;
+          reuse_par ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- MMA issuers: thread `me` owns the stages it = me, me + 2, ... and the accumulator
+    // columns [me * acc_cols, me * acc_cols + Mt); the two never read the same tile at once
+    const int me = warp - TC_PRODUCERS / 32;
+    if (lane == 0) {
+      const uint32_t idesc = tc_idesc_f16(TC_TILE_N, a.Mt);
+      const uint32_t a_k = (2 * (TC_TILE_N * 16)) >> 4, b_k = (2 * (a.Mt * 16)) >> 4;  // per 16 k
+      const uint32_t acc = tmem_base + (uint32_t)me * acc_cols;
+      for (int it = me; it < s1 - s0; it += 2) {
+        const int buf = it % NS;
+        const uint32_t par = (uint32_t)(it / NS) & 1u;
         if (!mbar_wait_bounded(&full[buf], par) || !mbar_wait_bounded(&bfull[buf], par)) {
           *abort_flag = 1;
           break;
@@ -459,26 +484,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         for (int j = 0; j < TC_KC / 16; ++j) {  // one MMA = 16 k-values = two core matrices in K
           const uint64_t ah = ah0 + (uint64_t)(j * a_k), al = al0 + (uint64_t)(j * a_k);
           const uint64_t bh = bh0 + (uint64_t)(j * b_k), bl = bl0 + (uint64_t)(j * b_k);
-          tc_mma_f16(tmem_base, ah, bh, idesc, (it > 0 || j > 0) ? 1u : 0u);  // wh * xh
-          tc_mma_f16(tmem_base, al, bh, idesc, 1u);                            // wl * xh
-          tc_mma_f16(tmem_base, ah, bl, idesc, 1u);                            // wh * xl
+          tc_mma_f16(acc, ah, bh, idesc, (it > me || j > 0) ? 1u : 0u);  // wh * xh
+          tc_mma_f16(acc, al, bh, idesc, 1u);                            // wl * xh
+          tc_mma_f16(acc, ah, bl, idesc, 1u);                            // wh * xl
         }
-        tc_commit(&done[buf]);
-        // B of stage s+NS-1 goes where the MMAs of stage s-1 read: wait for those (issued one
-        // iteration ago; the MMAs just issued keep the tensor pipe busy meanwhile)
-        if (s + NS - 1 < s1) {
-          if (it >= 1 && !mbar_wait_bounded(&done[prev], prev_par)) {
-            *abort_flag = 1;
-            break;
-          }
-          copy_b(s + NS - 1, prev);
-        }
-        prev = buf;
-        prev_par = par;
-        if (++buf == NS) {
-          buf = 0;
-          par ^= 1;
-        }
+        tc_commit(&done[buf]);  // frees the A and the B tile of the stage
       }
     }
     __syncwarp();
@@ -488,6 +498,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
   if (!failed && s1 > s0) {
     const int last = s1 - s0 - 1;
     failed = !mbar_wait_bounded(&done[last % NS], (uint32_t)(last / NS) & 1);
+    // the other issuer's last stage is the one before (its commits retire in its own order)
+    if (!failed && last >= 1)
+      failed = !mbar_wait_bounded(&done[(last - 1) % NS], (uint32_t)((last - 1) / NS) & 1);
   }
   failed = __syncthreads_or(failed);
   tc_fence_after();
@@ -496,15 +509,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     const int q = warp & 3;
     const int64_t n = n0 + q * 32 + lane;
     for (int c16 = warp >> 2; c16 < a.Mt / 16; c16 += TC_PRODUCERS / 128) {
-      uint32_t r[16];
-      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), r);
+      uint32_t r[16], r1[16];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16);
+      tmem_ld16(taddr, r);
+      if (s1 - s0 > 1) {
+        tmem_ld16(taddr + acc_cols, r1);  // the odd stages
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) r1[jj] = 0u;
+      }
       if (n < N) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
           const int m = c16 * 16 + jj;
           if (m < a.M) {
             float* dst = a.y[sg] + (int64_t)m * N + n;
-            const float v = __uint_as_float(r[jj]);
+            const float v = __uint_as_float(r[jj]) + __uint_as_float(r1[jj]);
             if (a.ksplit == 1)
               *dst = a.resid ? a.resid[(int64_t)m * N + n] + v : v;
             else
@@ -612,14 +632,14 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
   a.status = ctx->dev_status;
   const size_t per_stage = TC_A_STAGE + (size_t)(2 * 8 * Mt * 16);
   const size_t fixed = 96 + (size_t)TC_RAW_DEPTH * TC_RAW_STAGE;
-  // two A/B stages when that lets two CTAs share an SM (more warps to hide latency), else
-  // three stages if they fit
+  // Three A/B stages if they fit, else two, and one CTA per SM (the request is padded past half
+  // of the SM's shared memory where the stages alone would let two CTAs in): with two issuing
+  // threads per CTA a second CTA on the SM did not make the decode step faster (2209 us with two
+  // stages and two CTAs against 2177 us with three stages and one, 32 sequences).
   const size_t half_sm = ((size_t)ctx->smem_optin - 2048) / 2;
-  if (2 * per_stage + fixed <= half_sm)
-    a.nstage_smem = 2;
-  else
-    a.nstage_smem = 3 * per_stage + fixed <= (size_t)ctx->smem_optin ? 3 : 2;
-  const size_t smem = a.nstage_smem * per_stage + fixed;
+  a.nstage_smem = 3 * per_stage + fixed <= (size_t)ctx->smem_optin ? 3 : 2;
+  size_t smem = a.nstage_smem * per_stage + fixed;
+  if (smem <= half_sm + 1024) smem = half_sm + 2048;
   auto kern = dtype == KANSO_DTYPE_Q8_0 ? gemm_tc_kernel<TC_FMT_Q8_0> : gemm_tc_kernel<TC_FMT_Q4_K>;
   static bool attr_set[2][16] = {};
   bool& done = attr_set[dtype == KANSO_DTYPE_Q8_0 ? 0 : 1][ctx->device & 15];
