@@ -549,8 +549,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void* const* w,
                         float* const* y, const int64_t* rows, const float* x, const float* x2,
                         const float* norm_w, float eps, const float* resid, int64_t M, int64_t K,
-                        bool* handled) {
+                        bool* handled, const void* prepacked) {
+  // prepacked: x is already in the packed f16 hi/lo layout (written by the kernel before this
+  // one, e.g. the attention's merge); the pack launch is skipped. Only for a launch that has
+  // nothing else for the pack kernel to do (no norm, no SwiGLU, no output to clear).
   *handled = false;
+  if (prepacked && (x2 || norm_w)) return KANSO_OK;
   const int blk = dtype == KANSO_DTYPE_Q8_0 ? 32 : 256;
   if (nseg < 1 || nseg > TC_MAX_SEGS || (resid && nseg != 1)) return KANSO_OK;
   if (M < 1 || M > 128 || K < TC_KC || K % TC_KC != 0 || K % blk != 0) return KANSO_OK;
@@ -586,8 +590,10 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
   while (tiles_n * ksplit * 2 <= ctx->sm_count + ctx->sm_count / 4 &&
          stages_total / (ksplit * 2) >= 2)
     ksplit *= 2;
+  if (prepacked && ksplit > 1 && !(resid && resid == y[0])) return KANSO_OK;  // y needs a clear
   const size_t xp_bytes = 2 * (size_t)(K / 8) * Mt * 16;
-  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
+  uint8_t* scratch =
+      prepacked ? (uint8_t*)const_cast<void*>(prepacked) : (uint8_t*)ctx_scratch(ctx, xp_bytes + 256);
   if (!scratch) return KANSO_ERR_DEVICE;
   *handled = true;
 
@@ -611,8 +617,10 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
     }
   }
   const int64_t chunks = (K / 8) * Mt;
-  cudaError_t le;
-  if (norm_w)
+  cudaError_t le = cudaSuccess;
+  if (prepacked)
+    ;  // nothing to pack
+  else if (norm_w)
     le = launch_dependent(ctx, tc_pack_norm_kernel, dim3(Mt), dim3(256), 0, x, norm_w, eps,
                           reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, zero);
   else
@@ -620,7 +628,7 @@ int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void
                           dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, x, x2,
                           reinterpret_cast<__half*>(scratch), (int)M, Mt, (int)K, zero);
   if (le != cudaSuccess) return cuda_fail(ctx, le, "gemm_tc pack launch");
-  int32_t st = after_launch(ctx, "gemm_tc pack activations");
+  int32_t st = prepacked ? KANSO_OK : after_launch(ctx, "gemm_tc pack activations");
   if (st) return st;
   a.xp = reinterpret_cast<const __half*>(scratch);
   a.K = (int)K;
@@ -661,7 +669,7 @@ int32_t tc_matmul(kanso_cuda_ctx* ctx, int32_t dtype, const void* w, const float
   float* y1[1] = {y};
   const int64_t r1[1] = {N};
   return tc_matmul_multi(ctx, dtype, 1, w1, y1, r1, x, nullptr, nullptr, 0.f, nullptr, M, K,
-                         handled);
+                         handled, nullptr);
 }
 
 }  // namespace kanso

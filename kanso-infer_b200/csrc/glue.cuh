@@ -47,6 +47,10 @@ struct PaDecodeFusion {
   const float* cos_t;
   const float* sin_t;
   int table_len;
+  // Optional (batched decode): when not null the attention also writes its output as the packed
+  // f16 hi/lo activation tile of the o-projection's tensor-core GEMM and returns the tile here;
+  // it returns nullptr when it could not (the caller then packs the f32 output as usual).
+  const void** packed_out;
 };
 
 int32_t launch_silu_mul(kanso_cuda_ctx* ctx, const float* g, const float* u, float* out,

@@ -15,7 +15,7 @@ int32_t launch_paged_attention(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv, uin
 int32_t tc_matmul_multi(kanso_cuda_ctx* ctx, int32_t dtype, int nseg, const void* const* w,
                         float* const* y, const int64_t* rows, const float* x, const float* x2,
                         const float* norm_w, float eps, const float* resid, int64_t M, int64_t K,
-                        bool* handled);
+                        bool* handled, const void* prepacked);
 
 // Embedding rows of a Q8_0 table (src/weights.rs:50-57), bit-exact d * (f32)q.
 __global__ void model_embed_kernel(const uint8_t* __restrict__ w, const uint32_t* __restrict__ ids,
@@ -120,7 +120,8 @@ static int32_t ensure_ws(kanso_cuda_model* m, uint32_t B, uint32_t max_blocks) {
 // weights or shapes are outside that kernel's range: the caller then runs the pieces singly.
 static int32_t lin_multi(kanso_cuda_ctx* ctx, int n, const ModelLin* const* l, float* const* y,
                          const float* x, const float* x2, const float* norm_w, float eps,
-                         const float* resid, int64_t M, int32_t act_mode, bool* handled) {
+                         const float* resid, int64_t M, int32_t act_mode, bool* handled,
+                         const void* prepacked = nullptr) {
   *handled = false;
   if (act_mode != KANSO_ACT_F32 || M <= 8 || M > 128) return KANSO_OK;
   const void* w[3];
@@ -132,7 +133,7 @@ static int32_t lin_multi(kanso_cuda_ctx* ctx, int n, const ModelLin* const* l, f
   }
   if (l[0]->dtype != KANSO_DTYPE_Q8_0 && l[0]->dtype != KANSO_DTYPE_Q4_K) return KANSO_OK;
   return tc_matmul_multi(ctx, l[0]->dtype, n, w, y, rows, x, x2, norm_w, eps, resid, M,
-                         l[0]->cols, handled);
+                         l[0]->cols, handled, prepacked);
 }
 
 static int32_t lin(kanso_cuda_ctx* ctx, const ModelLin& l, const float* x, float* y, int64_t M,
@@ -387,14 +388,24 @@ int32_t kanso_cuda_decode_step_device(kanso_cuda_ctx* ctx, kanso_cuda_model* m, 
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_K], m->normed, k, B, act_mode))) return st;
       if ((st = lin(ctx, ly.w[KANSO_W_ATTN_V], m->normed, v, B, act_mode))) return st;
     }
+    // The attention's merge also leaves its output as the packed f16 tile of the o-projection's
+    // GEMM (when it can), which then starts without a pack launch of its own.
+    const void* packed = nullptr;
+    PaDecodeFusion fusion_l = fusion;
+    if (act_mode == KANSO_ACT_F32) fusion_l.packed_out = &packed;
     if ((st = launch_paged_attention(ctx, kv, l, q, block_tables, context_lens, m->attn, &pa,
-                                     max_ctx, &fusion)))
+                                     max_ctx, &fusion_l)))
       return st;
     {
       const ModelLin* l1[1] = {&ly.w[KANSO_W_ATTN_OUTPUT]};
       float* y1[1] = {m->hidden};
-      if ((st = lin_multi(ctx, 1, l1, y1, m->attn, nullptr, nullptr, 0.f, m->hidden, B, act_mode,
-                          &one)))
+      one = false;
+      if (packed &&
+          (st = lin_multi(ctx, 1, l1, y1, m->attn, nullptr, nullptr, 0.f, m->hidden, B, act_mode,
+                          &one, packed)))
+        return st;
+      if (!one && (st = lin_multi(ctx, 1, l1, y1, m->attn, nullptr, nullptr, 0.f, m->hidden, B,
+                                  act_mode, &one)))
         return st;
     }
     if (!one) {

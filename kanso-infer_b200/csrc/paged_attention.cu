@@ -61,7 +61,31 @@ struct PaArgs {
   const float* cos_t;  // [table_len][hd / 2]
   const float* sin_t;
   int table_len;
+  // Batched decode: the output is ALSO written as the f16 hi/lo activation tile that the
+  // o-projection's tensor-core GEMM reads (stage of 64 k-values, plane, k-chunk of 8, row:
+  // the layout of tc_pack_activations_kernel), which saves that GEMM its pack launch. xp_mt =
+  // rows of the tile (the batch rounded up to 16; the rows past the batch are zeroed here).
+  __half* xp;  // nullptr: off
+  uint32_t xp_mt;
 };
+
+// One output element into the packed tile: row = sequence, kk = head * head_dim + d.
+__device__ __forceinline__ void pa_store_packed(const PaArgs& a, uint32_t row, uint32_t kk,
+                                                float v) {
+  const __half hi = __float2half_rn(v);
+  const __half lo = __float2half_rn(v - __half2float(hi));
+  const uint32_t c = (kk >> 3) & 7u, e = kk & 7u;
+  __half* base = a.xp + (size_t)(kk >> 6) * (128u * a.xp_mt);
+  base[((size_t)c * a.xp_mt + row) * 8 + e] = hi;
+  base[((size_t)(8 + c) * a.xp_mt + row) * 8 + e] = lo;
+}
+// The tile's rows past the batch, for the k range of one KV head's query heads.
+__device__ __forceinline__ void pa_zero_packed_rows(const PaArgs& a, uint32_t rows, uint32_t k0,
+                                                    uint32_t nk, uint32_t tid, uint32_t nt) {
+  const uint32_t pad = a.xp_mt - rows;
+  for (uint32_t i = tid; i < pad * nk; i += nt)
+    pa_store_packed(a, rows + i / nk, k0 + i % nk, 0.f);
+}
 
 // (block, offset) of token i = i0, i0 + step, ... inside a partition, without a division per
 // token (the block size is a run-time value).
@@ -153,6 +177,12 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
     // the CPU statement leaves zeros (src/metal/paged_attention.rs:112-115)
     float* o = a.out + ((size_t)seq * a.num_heads + (size_t)kvh * G) * hd;
     for (uint32_t e = threadIdx.x; e < G * hd; e += NT) o[e] = 0.f;
+    if (a.xp) {
+      pdl_wait();  // the tile's last reader is an earlier kernel of the stream
+      for (uint32_t e = threadIdx.x; e < G * hd; e += NT)
+        pa_store_packed(a, seq, kvh * G * hd + e, 0.f);
+      if (seq == 0) pa_zero_packed_rows(a, gridDim.z, kvh * G * hd, G * hd, threadIdx.x, NT);
+    }
   }
   if (t0 >= ctx) return;
   const uint32_t n = min(a.part_tokens, ctx - t0);
@@ -222,6 +252,8 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
   // position of the newest token inside this partition (fused mode), else out of range
   const uint32_t i_new = (fused && ctx - 1 >= t0 && ctx - 1 < t0 + n) ? ctx - 1 - t0 : 0xFFFFFFFFu;
   if (fused) pdl_wait();  // q and the new K/V rows come from the kernel before this one
+  if (a.xp && seq == 0 && part == 0)
+    pa_zero_packed_rows(a, gridDim.z, kvh * G * hd, G * hd, threadIdx.x, NT);
 
   // --- stage the query heads of this group: warp w quantises heads w, w+4, ...
   constexpr int QE = PA_MAX_HEAD_DIM / 32;
@@ -505,7 +537,9 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
 #pragma unroll
       for (int k = 0; k < G; ++k)
         if (k == (int)gq) l = psum[k];
-      a.out[head * hd + d] = l > 0.f ? s / l : 0.f;
+      const float o = l > 0.f ? s / l : 0.f;
+      a.out[head * hd + d] = o;
+      if (a.xp) pa_store_packed(a, seq, (kvh * G + gq) * hd + d, o);
     } else {
       a.part_acc[(head * a.num_parts + part) * hd + d] = s;
     }
@@ -571,7 +605,9 @@ __global__ void __launch_bounds__(NT) paged_attn_stage1(const PaArgs a) {
         }
       }
     }
-    a.out[head * hd + d] = l > 0.f ? s / l : 0.f;
+    const float o = l > 0.f ? s / l : 0.f;
+    a.out[head * hd + d] = o;
+    if (a.xp) pa_store_packed(a, seq, (kvh * G + gq) * hd + d, o);
   }
 }
 
@@ -731,8 +767,19 @@ int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv
   const size_t nheads_total = (size_t)p->num_seqs * p->num_heads;
   const size_t acc_bytes = nheads_total * nparts * hd * sizeof(float);
   const size_t ml_bytes = nheads_total * nparts * 2 * sizeof(float);
-  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, acc_bytes + ml_bytes + 256);
+  // merge inside stage 1 when the ticket array covers the batch and the partition weights fit
+  // where the probabilities were
+  const bool merge_in_stage1 =
+      (uint64_t)p->num_seqs * p->num_kv_heads <= kanso_cuda_ctx::kPaTickets && nparts <= pt;
+  // the packed copy of the output for the o-projection (decode fusion only; 64 | heads * head_dim)
+  const uint32_t xp_mt = (p->num_seqs + 15u) / 16u * 16u;
+  const bool want_packed = fusion && fusion->packed_out && !row_seq && merge_in_stage1 &&
+                           (p->num_heads * hd) % 64 == 0;
+  const size_t xp_off = (acc_bytes + ml_bytes + 511) & ~size_t(255);
+  const size_t xp_bytes = want_packed ? 2 * (size_t)(p->num_heads * hd / 8) * xp_mt * 16 : 0;
+  uint8_t* scratch = (uint8_t*)ctx_scratch(ctx, xp_off + xp_bytes + 256);
   if (!scratch) return KANSO_ERR_DEVICE;
+  if (fusion && fusion->packed_out) *fusion->packed_out = want_packed ? scratch + xp_off : nullptr;
 
   PaArgs a;
   a.g = g;
@@ -749,11 +796,9 @@ int32_t launch_paged_attention_rows(kanso_cuda_ctx* ctx, const kanso_cuda_kv* kv
   a.num_parts = nparts;
   a.scale = p->scale;
   a.status = ctx->dev_status;
-  // merge inside stage 1 when the ticket array covers the batch and the partition weights fit
-  // where the probabilities were
-  const bool merge_in_stage1 =
-      (uint64_t)p->num_seqs * p->num_kv_heads <= kanso_cuda_ctx::kPaTickets && nparts <= pt;
   a.tickets = merge_in_stage1 ? ctx->pa_tickets : nullptr;
+  a.xp = want_packed ? reinterpret_cast<__half*>(scratch + xp_off) : nullptr;
+  a.xp_mt = xp_mt;
   a.row_seq = row_seq;
   a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
   a.positions = a.slots = nullptr;
@@ -1019,6 +1064,8 @@ static int32_t launch_paged_attention_static(kanso_cuda_ctx* ctx, const kanso_cu
   a.status = ctx->dev_status;
   a.tickets = nullptr;  // two launches: stage 2 merges
   a.row_seq = nullptr;
+  a.xp = nullptr;
+  a.xp_mt = 0;
   a.k_new = a.v_new = a.cos_t = a.sin_t = nullptr;
   a.positions = a.slots = nullptr;
   a.table_len = 0;
